@@ -312,6 +312,106 @@ class FopivikConfig:
         return self.max_position
 
 
+def _rot_of(m, where: str, limit: int):
+    rot = _take(m, "rot", dict)
+    dims, base = _take(rot, "dims", int), _take(rot, "base", float)
+    if dims < 0 or dims % 2 or dims > limit or not base > 0:
+        raise ConfigError(f"config.json: {where}.rot: dims must be even and at most {limit}, base positive")
+    return dims, base
+
+
+@dataclass(frozen=True)
+class NorusunConfig:
+    """config.json of a Norusun folder: a decoder whose layers are listed one by one, on a residual stream that is
+    kept as several copies (hyper-connections), every mixer reading its input through a short causal convolution.
+
+    Top level: `architecture`, `width`, `vocab`, `norm.eps`, `streams`, `canon.taps`, `layers`.  A layer gives `type`
+    (its mixer), `mixer` and `mlp` ({kind: dense, ff, limit} or null).
+      wkv               heads, dim
+      latent_attention  heads, dim, rot_dim, vdim, kv_rank, q_rank, scale, mask.size, rot {dims, base}
+      parallel          left  {heads, kv_heads, dim, vdim, scale, mask.size, rot {dims, base}}
+                        right {heads, vdim, state, groups, norm_groups, conv}
+    The design has no length limit of its own: max_position (optional) bounds what the engine sizes its tables for."""
+
+    architecture: str
+    width: int
+    vocab: int
+    norm_eps: float
+    streams: int
+    canon_taps: int
+    layers: tuple                      # of dicts, validated
+    max_position: int = 131072
+    eos_token_id: Optional[int] = None
+
+    MIXERS = ("wkv", "latent_attention", "parallel")
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "NorusunConfig":
+        norm = _take(d, "norm", dict)
+        layers = _take(d, "layers", list)
+        if not layers:
+            raise ConfigError("config.json: 'layers' must list at least one layer")
+        out = []
+        for i, layer in enumerate(layers):
+            where = f"layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"config.json: {where} must be an object")
+            kind = _take(layer, "type", str)
+            m = _take(layer, "mixer", dict)
+            if kind == "wkv":
+                mixer = {k: _take(m, k, int) for k in ("heads", "dim")}
+                if min(mixer.values()) <= 0:
+                    raise ConfigError(f"config.json: {where}.mixer: sizes must be positive")
+            elif kind == "latent_attention":
+                mixer = {k: _take(m, k, int) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank")}
+                mixer["scale"] = _take(m, "scale", float)
+                mixer["window"] = _take(_take(m, "mask", dict), "size", int)
+                if min(mixer[k] for k in ("heads", "dim", "vdim", "kv_rank", "q_rank", "window")) <= 0 or mixer["rot_dim"] < 0 \
+                        or mixer["rot_dim"] % 2:
+                    raise ConfigError(f"config.json: {where}.mixer: sizes must be positive and rot_dim even")
+                mixer["rot_dims"], mixer["rot_base"] = _rot_of(m, where + ".mixer", mixer["rot_dim"])
+            elif kind == "parallel":
+                left, right = _take(m, "left", dict), _take(m, "right", dict)
+                a = {k: _take(left, k, int) for k in ("heads", "kv_heads", "dim", "vdim")}
+                a["scale"] = _take(left, "scale", float)
+                a["chunk"] = _take(_take(left, "mask", dict), "size", int)
+                if min(a[k] for k in ("heads", "kv_heads", "dim", "vdim", "chunk")) <= 0 or a["heads"] % a["kv_heads"]:
+                    raise ConfigError(f"config.json: {where}.mixer.left: sizes must be positive and heads a multiple of kv_heads")
+                a["rot_dims"], a["rot_base"] = _rot_of(left, where + ".mixer.left", a["dim"])
+                b = {k: _take(right, k, int) for k in ("heads", "vdim", "state", "groups", "norm_groups", "conv")}
+                if min(b.values()) <= 0 or b["heads"] % b["groups"] or (b["heads"] * b["vdim"]) % b["norm_groups"]:
+                    raise ConfigError(f"config.json: {where}.mixer.right: sizes must be positive, heads a multiple of groups "
+                                      f"and heads * vdim a multiple of norm_groups")
+                mixer = {"left": a, "right": b}
+            else:
+                raise ConfigError(f"config.json: {where}.type '{kind}' is not a mixer of this design {cls.MIXERS}")
+            ff = layer.get("mlp")
+            mlp = None
+            if ff is not None:
+                if not isinstance(ff, dict):
+                    raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+                if _take(ff, "kind", str) != "dense":
+                    raise ConfigError(f"config.json: {where}.mlp.kind '{ff['kind']}' is not 'dense'")
+                mlp = {"kind": "dense", "ff": _take(ff, "ff", int), "limit": _take(ff, "limit", float)}
+                if mlp["ff"] <= 0 or not mlp["limit"] > 0:
+                    raise ConfigError(f"config.json: {where}.mlp: ff and limit must be positive")
+            out.append({"type": kind, "mixer": mixer, "mlp": mlp})
+        eos = d.get("eos_token_id")
+        cfg = cls(architecture=_take(d, "architecture", str), width=_take(d, "width", int), vocab=_take(d, "vocab", int),
+                  norm_eps=_take(norm, "eps", float), streams=_take(d, "streams", int),
+                  canon_taps=_take(_take(d, "canon", dict), "taps", int), layers=tuple(out),
+                  max_position=_take(d, "max_position", int, 131072), eos_token_id=eos if isinstance(eos, int) else None)
+        if cfg.width <= 0 or cfg.vocab <= 0 or cfg.max_position <= 0:
+            raise ConfigError("config.json: width, vocab and max_position must be positive")
+        if not (1 <= cfg.streams <= 8) or not (1 <= cfg.canon_taps <= 16):
+            raise ConfigError("config.json: streams must be 1 to 8 and canon.taps 1 to 16")
+        return cfg
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_position
+
+
 @dataclass(frozen=True)
 class Architecture:
     """One registry entry: how to read the config and how to lay the model out."""

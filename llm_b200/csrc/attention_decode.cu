@@ -63,7 +63,8 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
                         const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                         const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ kv_lens, int n_heads, int n_kv, int head_dim_arg, int page_size,
-                        int window, float scale, int splits, float softcap, int sink, int keep_first) {
+                        int window, float scale, int splits, float softcap, int sink, int keep_first,
+                        const float* __restrict__ sink_values) {
   constexpr bool STAGE_V = HS > 0;
   constexpr int QW = HS > 0 ? HS : MAX_HS;
   constexpr int V_PITCH = HS + 16 / (int)sizeof(T);                 // elements; rows stay 16-byte aligned
@@ -295,9 +296,10 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
       for (int i = tid; i < nh * head_dim; i += THREADS) {
         const int h = i / head_dim, d = i % head_dim;
         // the sink joins the denominator with weight exp(0 - m); above m = 0 the row is rescaled to it first
-        const float m_ref = sink ? fmaxf(m_s[h], 0.f) : m_s[h];
+        const float sv = (sink && sink_values) ? sink_values[head0 + h] : 0.f;      // the sink's score: a number per head, or 0
+        const float m_ref = sink ? fmaxf(m_s[h], sv) : m_s[h];
         const float w = sink ? expf(m_s[h] - m_ref) : 1.f;
-        const float denom = l_s[h] * w + (sink ? expf(-m_ref) : 0.f);
+        const float denom = l_s[h] * w + (sink ? expf(sv - m_ref) : 0.f);
         out[(size_t)e * out_stride + (size_t)(head0 + h) * head_dim + d] = from_f32<T>(o_sum[i] * w / denom);
       }
     } else {
@@ -339,9 +341,10 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
     }
     __syncthreads();
     if (tid < nh) {                                                     // weights exp(m_s - m) / l, from shared memory only
-      float m = sink ? 0.f : -INFINITY;               // the sink is one more range: maximum 0, sum 1, no values
+      const float sv = (sink && sink_values) ? sink_values[g * group + h0 + tid] : 0.f;
+      float m = sink ? sv : -INFINITY;                // the sink is one more range: maximum its score (0 unless given), sum 1, no values
       for (int sp = 0; sp < n_active; ++sp) m = fmaxf(m, w_s[tid * splits + sp]);
-      float l = sink ? expf(-m) : 0.f;
+      float l = sink ? expf(sv - m) : 0.f;
       for (int sp = 0; sp < n_active; ++sp) {
         const float wgt = expf(w_s[tid * splits + sp] - m);
         l += wgt * l_in[tid * splits + sp];
@@ -387,7 +390,7 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
                                          int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
                                          int head_dim, int page_size, int window, float scale, int splits,
                                          float* scratch, int dtype, cudaStream_t stream, float softcap, int sink,
-                                         int keep_first) {
+                                         int keep_first, const float* sink_values) {
   if (n_entries == 0) return 0;
   LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_decode: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
   if (window == 0) keep_first = 0;
@@ -407,7 +410,7 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
     if (head_dim == 128) kern = decode_attention_kernel<T, 128>;
     launch_kernel(kern, grid, dim3(THREADS), 0, stream, (T*)out, out_stride, scratch, (const T*)q, q_stride,
                   (const T*)k_pages, (const T*)v_pages, block_table, table_width, kv_lens, n_heads, n_kv, head_dim,
-                  page_size, window, scale, splits, softcap, sink, keep_first);
+                  page_size, window, scale, splits, softcap, sink, keep_first, sink_values);
     LLMK_LAUNCH_CHECK("attention_decode");
   });
 }
@@ -461,5 +464,5 @@ LLMK_API int llmk_paged_attention_decode_static(void* out, long long out_stride,
   if (rc) return rc;
   return llmk_paged_attention_decode(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
                                      n_entries, n_heads, n_kv, head_dim, page_size, window, scale, splits, scratch,
-                                     dtype, stream, 0.f, 0, 0);
+                                     dtype, stream, 0.f, 0, 0, nullptr);
 }

@@ -12,7 +12,10 @@
 // kernels refuse.  Options, all off at zero: values of another size than the keys (vdim); a soft cap
 // on the scaled scores, s <- cap * tanh(s / cap); a sink, a key with score 0 and no value that only
 // adds 1 to the softmax's denominator; and, with a window, the first keep_first keys of the request,
-// which stay visible (at their true positions) after the window has passed them.
+// which stay visible (at their true positions) after the window has passed them.  Further: the sink's score may be a
+// learned number per head (sink_values; it is not scaled); the mask may be by chunks instead of a window (chunk > 0: a
+// query sees the keys at or before it whose position has the same floor(position / chunk)); and the weights may be
+// sigmoid(score + bias[head]) without a softmax (sigmoid_bias given: no maximum, no normalisation, no sink).
 #include "common.cuh"
 
 namespace {
@@ -70,7 +73,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                int table_width, const int* __restrict__ token_entry,
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
                                int head_dim, int vdim, int page_size, int window, int keep_first, float scale,
-                               float softcap, int sink, bool vec) {
+                               float softcap, int sink, bool vec, const float* __restrict__ sink_values, int chunk,
+                               const float* __restrict__ sigmoid_bias) {
   __shared__ float q_s[WARPS][MAXD];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
@@ -81,7 +85,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   const int g = h / (n_heads / n_kv);
   const int pos = positions[t];
   const int* table = block_table + (size_t)token_entry[t] * table_width;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int keep_end = min(keep_first, lo);      // keys [0, keep_end) lie before the window and are seen all the same
   const int lo_tile = (lo / 32) * 32;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
@@ -94,7 +98,9 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
 #pragma unroll
   for (int i = 0; i < MAXD / 32; ++i) acc[i] = 0.f;
   // the sink is the first term of the softmax: score 0, weight exp(0 - m), no value
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+  const bool gated = sigmoid_bias != nullptr;
+  const float bias = gated ? sigmoid_bias[h] : 0.f;
+  float m = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
 
   for (int tile = keep_end > 0 ? 0 : lo_tile; tile <= pos; tile += 32) {
     if (tile >= keep_end && tile < lo_tile) {      // between the kept keys and the window: nothing to see
@@ -112,13 +118,18 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
       s = (vec ? dot_row<T>(q_s[warp], k_row, head_dim) : dot_row_scalar<T>(q_s[warp], k_row, head_dim)) * scale;
       if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float alpha = expf(m - m_new);  // m = -inf at the first tile gives 0
-    const float p = valid ? expf(s - m_new) : 0.f;
-    l = l * alpha + warp_sum(p);
-    m = m_new;
+    float p;
+    if (gated) {
+      p = valid ? 1.f / (1.f + expf(-(s + bias))) : 0.f;
+    } else {
+      const float m_new = fmaxf(m, warp_max(s));
+      const float alpha = expf(m - m_new);  // m = -inf at the first tile gives 0
+      p = valid ? expf(s - m_new) : 0.f;
+      l = l * alpha + warp_sum(p);
+      m = m_new;
 #pragma unroll
-    for (int i = 0; i < MAXD / 32; ++i) acc[i] *= alpha;
+      for (int i = 0; i < MAXD / 32; ++i) acc[i] *= alpha;
+    }
     const int n_valid = min(32, pos - tile + 1);
     for (int j = 0; j < n_valid; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
@@ -133,7 +144,7 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
       }
     }
   }
-  const float inv = 1.f / l;
+  const float inv = gated ? 1.f : 1.f / l;
   T* o = out + (size_t)t * out_stride + (size_t)h * vdim;
 #pragma unroll
   for (int i = 0; i < MAXD / 32; ++i) {
@@ -152,7 +163,7 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
                                           int table_width, const int* token_entry, const int* positions,
                                           int n_tokens, int n_heads, int n_kv, int head_dim, int vdim, int page_size,
                                           int window, int keep_first, float scale, float softcap, int sink, int dtype,
-                                          cudaStream_t stream) {
+                                          cudaStream_t stream, const float* sink_values, int chunk, const float* sigmoid_bias) {
   if (n_tokens == 0) return 0;
   LLMK_REQUIRE(head_dim > 0 && head_dim <= MAX_HEAD_DIM, "paged_attention: head_dim %d must be 1 to %d", head_dim, MAX_HEAD_DIM);
   LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "paged_attention: %d query heads do not divide into %d kv heads",
@@ -160,6 +171,8 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
   LLMK_REQUIRE(vdim > 0 && vdim <= MAX_HEAD_DIM, "paged_attention: value size %d must be 1 to %d", vdim, MAX_HEAD_DIM);
   LLMK_REQUIRE(page_size > 0 && window >= 0, "paged_attention: bad page_size %d or window %d", page_size, window);
   LLMK_REQUIRE(keep_first >= 0 && softcap >= 0.f, "paged_attention: bad keep_first %d or soft cap %f", keep_first, (double)softcap);
+  LLMK_REQUIRE(chunk >= 0 && !(chunk > 0 && keep_first > 0), "paged_attention: bad chunk %d", chunk);
+  if (sigmoid_bias) sink = 0;
   if (window == 0) keep_first = 0;
   const int widest = head_dim > vdim ? head_dim : vdim;
   const long long items = (long long)n_tokens * n_heads;
@@ -172,17 +185,17 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
       launch_kernel(paged_attention_generic_kernel<T, 256>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
     else if (widest <= 512)      // the wide head of a latent attention (its rank)
       launch_kernel(paged_attention_generic_kernel<T, 512>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
     else
       launch_kernel(paged_attention_generic_kernel<T, MAX_HEAD_DIM>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
     LLMK_LAUNCH_CHECK("paged_attention_generic");
   });
 }

@@ -42,6 +42,16 @@ def _split_args(x):
     return _ptr(x), c_void_p(0), c_int(0), c_longlong(0)
 
 
+def settle(x, out: torch.Tensor, rows: int) -> torch.Tensor:
+    """x itself if it is a tensor; the sum of a PartialSum's splits, written to out[:rows] (contiguous), otherwise."""
+    if not isinstance(x, PartialSum):
+        return x
+    assert out.is_contiguous() and out.shape[-1] == x.cols and x.rows == rows
+    _check_t(load_tensor().llmk_reduce_partials(_ptr(out), c_void_p(x.buf.data_ptr()), c_longlong(rows * x.cols), c_int(x.splits),
+                                                c_int(_kind(out.dtype)), _stream()))
+    return out
+
+
 def _kind(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return _F32
@@ -271,7 +281,8 @@ def gla_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
         count_launches(3)
 
 
-ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
+ACTIVATIONS = {"relu2": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3, "tanh": 4}
+EPILOGUE_ACTIVATIONS = ("relu2", "gelu", "gelu_tanh", "silu")      # those the product kernels apply in their epilogues
 
 
 def act_rows(out: torch.Tensor, x, rows: int, kind: str) -> None:
@@ -326,6 +337,241 @@ def latent_norm_store(x: torch.Tensor, gain: torch.Tensor, eps: float, slot_map:
     assert gain.dtype == torch.float32 and slot_map.dtype == torch.int32
     _check(load().llmk_latent_norm_store(_ptr(x), c_longlong(x.stride(0)), _ptr(gain), c_float(eps), _ptr(slot_map),
                                          _ptr(pages), c_int(n_tokens), c_int(rank), c_int(width), c_int(_kind(x.dtype)), _stream()))
+
+
+# ---- hyper-connections (hyper.cu) -------------------------------------------------------
+
+def hc_embedding(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int, streams: int,
+                 status: torch.Tensor) -> None:
+    """resid[:n_tokens] (float32 [.., streams * hidden]): every stream of a token = table[ids]; an id outside the table
+    sets status[0]."""
+    vocab, hidden = table.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[-1] == streams * hidden
+    assert ids.dtype == torch.int32 and status.dtype == torch.int32 and table.is_contiguous()
+    _check(load().llmk_hc_embedding(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens), c_int(hidden), c_int(vocab),
+                                    c_int(streams), c_int(_kind(table.dtype)), _ptr(status), _stream()))
+
+
+def hc_norm(resid: torch.Tensor, y, write_mix, write_out, read_in, gain, out, rows: int, hidden: int, streams: int,
+            eps: float, dtype: torch.dtype) -> None:
+    """The streams of resid[:rows] (float32 [.., streams * hidden]) first take the pending write, if y is given (a tensor
+    or a PartialSum [rows, hidden]): x_t <- sum_s write_mix[s, t] x_s + write_out[t] y; then, if out is given,
+    out[:rows] = rms(sum_s read_in[s] x_s) * gain (gain one float32 number).  All weights float32 on the device."""
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[-1] == streams * hidden
+    for t, n in ((write_mix, streams * streams), (write_out, streams), (read_in, streams), (gain, 1)):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
+    if isinstance(y, PartialSum):
+        assert y.cols == hidden and y.rows == rows
+    elif y is not None:
+        assert y.is_contiguous() and y.shape[-1] == hidden and y.dtype == dtype
+    if out is not None:
+        assert out.is_contiguous() and out.shape[-1] == hidden and out.dtype == dtype
+    if y is None and out is None:
+        return
+    d, parts, splits, stride = _split_args(y)
+    _check(load().llmk_hc_norm(_ptr(resid), d, parts, splits, stride, _ptr(write_mix if y is not None else None),
+                               _ptr(write_out if y is not None else None), _ptr(read_in), _ptr(gain), _ptr(out), c_int(rows),
+                               c_int(hidden), c_int(streams), c_float(eps), c_int(_kind(dtype)), _stream()))
+
+
+def hc_gather_sum(out: torch.Tensor, resid: torch.Tensor, rows: torch.Tensor, n_rows: int, streams: int) -> None:
+    """out[r] = the sum over the streams of resid[rows[r]], float32."""
+    hidden = out.shape[-1]
+    assert out.dtype == resid.dtype == torch.float32 and rows.dtype == torch.int32 and resid.shape[-1] == streams * hidden
+    _check(load().llmk_hc_gather_sum(_ptr(out), _ptr(resid), _ptr(rows), c_int(n_rows), c_int(hidden), c_int(streams), _stream()))
+
+
+def scalar_rmsnorm_rows(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, n_rows: int, eps: float) -> None:
+    """out[:n_rows] = x / sqrt(mean(x^2) + eps) * gain for float32 rows x and one float32 number gain."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == x.shape[-1]
+    assert gain.dtype == torch.float32 and gain.numel() == 1
+    _check(load().llmk_scalar_rmsnorm_rows(_ptr(out), _ptr(x), _ptr(gain), c_int(n_rows), c_int(x.shape[-1]), c_float(eps),
+                                           c_int(_kind(out.dtype)), _stream()))
+
+
+# ---- short convolution (short_conv.cu) ----------------------------------------------------
+
+def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias, state: torch.Tensor, ctx, residual: bool = False,
+               silu: bool = False) -> None:
+    """out[t] = conv(x)_t (+ x_t if residual; silu of it if asked) over every entry's tokens, the entry's last taps - 1
+    inputs before this step read from, and afterwards kept in, state [slots, >= (taps - 1) * channels] float32 (rows may be
+    strided: a column range of a wider state).  w float32 [channels, taps]; bias float32 [channels] or None."""
+    _rows_contig(out, "out"); _rows_contig(x, "x"); _rows_contig(state, "state")
+    channels, taps = w.shape
+    assert x.shape[1] == out.shape[1] == channels and x.dtype == out.dtype
+    assert w.dtype == torch.float32 and w.is_contiguous() and state.dtype == torch.float32
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == channels)
+    assert state.shape[1] >= (taps - 1) * channels
+    _check(load().llmk_short_conv(_ptr(out), c_longlong(out.stride(0)), _ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias),
+                                  _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.token_entry),
+                                  _ptr(ctx.cu_tokens), c_int(ctx.n_tokens), c_int(ctx.n_entries), c_int(channels), c_int(taps),
+                                  c_int(int(residual)), c_int(int(silu)), c_int(_kind(x.dtype)), _stream()))
+    if taps > 1:
+        count_launches(1)
+
+
+# ---- recurrences with a diagonal decay (scan.cu) ------------------------------------------
+
+def token_shift(out: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx) -> None:
+    """out[t, m*W:(m+1)*W] = h_t + (h_(t-1) - h_t) * mu[m] for every mix m; the row before an entry's first token is
+    state[slot] (float32 [slots, >= W], zero at admission; the recurrence kernel that follows renews it)."""
+    _rows_contig(out, "out"); _rows_contig(h, "h"); _rows_contig(state, "state")
+    mixes, width = mu.shape
+    assert h.shape[1] == width and out.shape[1] == mixes * width and out.dtype == h.dtype
+    assert mu.dtype == state.dtype == torch.float32 and mu.is_contiguous() and state.shape[1] >= width
+    _check(load().llmk_token_shift(_ptr(out), c_longlong(out.stride(0)), _ptr(h), c_longlong(h.stride(0)), _ptr(mu), _ptr(state),
+                                   c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.token_entry), _ptr(ctx.cu_tokens),
+                                   c_int(ctx.n_tokens), c_int(width), c_int(mixes), c_int(_kind(h.dtype)), _stream()))
+
+
+def wkv_scan(out: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor,
+             bonus: torch.Tensor, state: torch.Tensor, ctx, shift_src=None, shift_state=None) -> None:
+    """o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(exp(-exp(z_t + z_bias))) S_(t-1) + k_t v_t^T per head (scan.cu).
+    r, k, v [T, heads*dim]: column ranges of one projection; z float32 [T, heads*dim]; bonus float32 [heads, dim];
+    state float32 [slots, >= heads*dim*dim]; out float32 [T, heads*dim].  shift_src [T, W] / shift_state [slots, >= W]:
+    the last row of every entry is kept there for the next step's token shift."""
+    for t in (out, r, k, v, z, state):
+        _rows_contig(t, "wkv operand")
+    heads, dim = bonus.shape
+    assert r.stride(0) == k.stride(0) == v.stride(0) and r.dtype == k.dtype == v.dtype
+    assert r.shape[1] == k.shape[1] == v.shape[1] == z.shape[1] == out.shape[1] == heads * dim
+    assert z.dtype == out.dtype == state.dtype == bonus.dtype == z_bias.dtype == torch.float32
+    assert bonus.is_contiguous() and z_bias.numel() == heads * dim and state.shape[1] >= heads * dim * dim
+    width = 0
+    if shift_src is not None:
+        _rows_contig(shift_src, "shift_src"); _rows_contig(shift_state, "shift_state")
+        width = shift_src.shape[1]
+        assert shift_src.dtype == r.dtype and shift_state.dtype == torch.float32 and shift_state.shape[1] >= width
+    _check(load().llmk_wkv_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(r), _ptr(k), _ptr(v), c_longlong(r.stride(0)), _ptr(z),
+                                c_longlong(z.stride(0)), _ptr(z_bias), _ptr(bonus), _ptr(state), c_longlong(state.stride(0)),
+                                _ptr(ctx.state_slots), _ptr(ctx.cu_tokens), c_int(ctx.n_entries), c_int(heads), c_int(dim),
+                                _ptr(shift_src), c_longlong(shift_src.stride(0) if shift_src is not None else 0), _ptr(shift_state),
+                                c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width),
+                                c_int(_kind(r.dtype)), _stream()))
+
+
+def ssd_scan(out: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor,
+             a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, ctx, heads: int, groups: int, dim: int, vdim: int) -> None:
+    """S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + skip x_t per head, dt_t = softplus(dt + dt_bias),
+    a_t = exp(-exp(a_log) dt_t) (scan.cu).  x [T, heads*vdim], b and c [T, groups*dim] (one row stride), dt [T, heads];
+    dt_bias, a_log, skip float32 [heads]; state float32 [slots, >= heads*dim*vdim]; out float32 [T, heads*vdim]."""
+    for t in (out, x, b, c, dt, state):
+        _rows_contig(t, "ssd operand")
+    assert b.stride(0) == c.stride(0) and x.dtype == b.dtype == c.dtype == dt.dtype
+    assert x.shape[1] == out.shape[1] == heads * vdim and b.shape[1] == c.shape[1] == groups * dim and dt.shape[1] == heads
+    assert out.dtype == state.dtype == torch.float32 and state.shape[1] >= heads * dim * vdim
+    for t in (dt_bias, a_log, skip):
+        assert t.dtype == torch.float32 and t.numel() == heads
+    _check(load().llmk_ssd_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(x), c_longlong(x.stride(0)), _ptr(b), _ptr(c),
+                                c_longlong(b.stride(0)), _ptr(dt), c_longlong(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip),
+                                _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.cu_tokens),
+                                c_int(ctx.n_entries), c_int(heads), c_int(groups), c_int(dim), c_int(vdim), c_int(_kind(x.dtype)),
+                                _stream()))
+
+
+def group_rmsnorm_gate(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, rows: int, groups: int,
+                       eps: float, gate_first: bool = False) -> None:
+    """Per group of channels g: out = rms(x_g) * w_g * silu(gate_g), or with gate_first rms(x_g * silu(gate_g)) * w_g.
+    x float32 [rows, groups * n] contiguous; w float32 [groups * n]; gate in out's dtype, rows may be strided."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == x.shape[-1]
+    n = x.shape[-1] // groups
+    assert n * groups == x.shape[-1] and w.dtype == torch.float32 and w.numel() == x.shape[-1]
+    _rows_contig(gate, "gate")
+    assert gate.dtype == out.dtype and gate.shape[1] == x.shape[-1]
+    _check(load().llmk_group_rmsnorm_gate(_ptr(out), _ptr(x), _ptr(w), _ptr(gate), c_longlong(gate.stride(0)), c_int(rows),
+                                          c_int(groups), c_int(n), c_float(eps), c_int(int(gate_first)), c_int(_kind(out.dtype)),
+                                          _stream()))
+
+
+def pair_norm_mean(out: torch.Tensor, a, b, wa: torch.Tensor, wb: torch.Tensor, rows: int, eps: float) -> None:
+    """out[:rows] = (rms(a) * wa + rms(b) * wb) / 2 row by row; a and b tensors or PartialSums [rows, width]."""
+    width = out.shape[-1]
+    assert out.is_contiguous() and wa.dtype == wb.dtype == torch.float32 and wa.numel() == wb.numel() == width
+    for t in (a, b):
+        if isinstance(t, PartialSum):
+            assert t.cols == width and t.rows == rows
+        else:
+            assert t.is_contiguous() and t.shape[-1] == width and t.dtype == out.dtype
+    da, pa, sa, sta = _split_args(a)
+    db, pb, sb, stb = _split_args(b)
+    _check(load().llmk_pair_norm_mean(_ptr(out), da, pa, sa, sta, db, pb, sb, stb, _ptr(wa), _ptr(wb), c_int(rows), c_int(width),
+                                      c_float(eps), c_int(_kind(out.dtype)), _stream()))
+
+
+def clamped_glu(out: torch.Tensor, gate_up, bias, rows: int, limit: float, alpha: float) -> None:
+    """out[:rows, :I] = g * sigmoid(alpha g) * (u + 1), g = min(gate + b, limit), u = clamp(up + b, -limit, limit), for
+    gate_up = [gate | up] (a tensor or a PartialSum [rows, 2 I]) and bias float32 [2 I] or None."""
+    inter = out.shape[-1]
+    assert out.is_contiguous() and out.dtype == gate_up.dtype
+    if isinstance(gate_up, PartialSum):
+        assert gate_up.cols == 2 * inter and gate_up.rows == rows
+    else:
+        assert gate_up.shape[-1] == 2 * inter and gate_up.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inter)
+    d, parts, splits, stride = _split_args(gate_up)
+    _check(load().llmk_clamped_glu(_ptr(out), d, parts, splits, stride, _ptr(bias), c_int(rows), c_int(inter), c_float(limit),
+                                   c_float(alpha), c_int(_kind(out.dtype)), _stream()))
+
+
+def latent_rope_norm_store(x: torch.Tensor, q_gain, q_rank: int, cq_out, gain: torch.Tensor, rot: int, freqs, positions,
+                           eps: float, slot_map, pages, n_tokens: int) -> None:
+    """x float32 [T, q_rank + rank + rot]: cq_out[t] = rms(x[:q_rank]) * q_gain (if q_rank), and the token's cache row
+    pages[slot_map[t]] = [the rot last numbers with pairs (2i, 2i+1), i < len(freqs), turned by position * freqs[i] |
+    rms(the rank numbers between) * gain | zeros]; pages None: no row is written."""
+    _rows_contig(x, "x")
+    rank = gain.numel()
+    assert x.dtype == torch.float32 and x.shape[1] >= q_rank + rank + rot and gain.dtype == torch.float32
+    pairs = 0 if freqs is None else freqs.numel()
+    assert freqs is None or (freqs.dtype == torch.float32 and freqs.is_contiguous())
+    kind = None
+    if q_rank:
+        _rows_contig(cq_out, "cq_out")
+        assert q_gain.dtype == torch.float32 and q_gain.numel() == q_rank and cq_out.shape[1] >= q_rank
+        kind = cq_out.dtype
+    width = 0
+    if pages is not None:
+        assert pages.is_contiguous() and pages.shape[1] == 1 and slot_map.dtype == torch.int32
+        assert kind is None or kind == pages.dtype
+        kind, width = pages.dtype, pages.shape[3]
+    _check(load().llmk_latent_rope_norm_store(_ptr(x), c_longlong(x.stride(0)), _ptr(q_gain), c_int(q_rank), _ptr(cq_out),
+                                              c_longlong(cq_out.stride(0) if cq_out is not None else 0), _ptr(gain), c_int(rank),
+                                              c_int(rot), _ptr(freqs), c_int(pairs), _ptr(positions), c_float(eps), _ptr(slot_map),
+                                              _ptr(pages), c_int(n_tokens), c_int(width), c_int(_kind(kind)), _stream()))
+
+
+def norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, freqs, halves: bool, positions: torch.Tensor, slot_map, k_pages, v_pages,
+                       n_tokens: int, n_heads: int, n_kv: int, dim: int, vdim: int, q_out=None) -> torch.Tensor:
+    """As rope_pairs_kv_write, with the RMS norm of the token's whole q projection (weights q_gain, float32
+    [n_heads * dim]) and whole k projection (k_gain [n_kv * dim]) first, either None for none, and the choice of pairs:
+    halves turns channel i against channel i + len(freqs), else 2i against 2i + 1.  Returns the tensor that holds q."""
+    assert positions.dtype == torch.int32
+    width = n_heads * dim + n_kv * (dim + vdim)
+    if isinstance(qkv, PartialSum):
+        assert q_out is not None and qkv.cols >= width
+        src_stride = qkv.cols
+    else:
+        _rows_contig(qkv, "qkv")
+        assert qkv.shape[1] >= width
+        src_stride = qkv.stride(0)
+        if q_out is None:
+            q_out = qkv
+    _rows_contig(q_out, "q_out")
+    assert q_out.dtype == qkv.dtype
+    page = 1
+    if n_kv:
+        assert slot_map.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+        assert k_pages.shape[1] == n_kv and k_pages.shape[3] == dim and v_pages.shape[3] == vdim
+        page = k_pages.shape[2]
+    pairs = 0 if freqs is None else freqs.numel()
+    for t, n in ((q_gain, n_heads * dim), (k_gain, n_kv * dim), (freqs, pairs)):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
+    d, parts, splits, stride = _split_args(qkv)
+    _check(load().llmk_norm_rope_kv_write(d, parts, splits, stride, c_longlong(src_stride), _ptr(q_out), c_longlong(q_out.stride(0)),
+                                          _ptr(q_gain), _ptr(k_gain), c_float(eps), _ptr(freqs), c_int(pairs), c_int(int(halves)),
+                                          _ptr(positions), _ptr(slot_map), _ptr(k_pages), _ptr(v_pages), c_int(n_tokens),
+                                          c_int(n_heads), c_int(n_kv), c_int(dim), c_int(vdim), c_int(page), c_int(_kind(qkv.dtype)),
+                                          _stream()))
+    return q_out
 
 
 @functools.lru_cache(maxsize=None)
@@ -514,10 +760,15 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.T
                             block_table: torch.Tensor, token_entry: torch.Tensor, positions: torch.Tensor,
                             n_tokens: int, n_heads: int, n_kv: int, head_dim: int, window: int,
                             scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
-                            keep_first: int = 0) -> None:
+                            keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None) -> None:
     """out[t, h*VS:(h+1)*VS] = causal (windowed) attention of q[t, h] over its request's pages.  value_dim: size of a
     value row where it differs from the keys' (0 = the same); softcap > 0: scores pass cap * tanh(s / cap); sink: the
-    softmax's denominator gets one more term of score 0; keep_first: with a window, the request's first keys stay visible."""
+    softmax's denominator gets one more term of score 0, or of score sink_values[h] (float32 [heads], not scaled);
+    keep_first: with a window, the request's first keys stay visible; chunk > 0: instead of a window, a query sees the
+    keys at or before it with the same floor(position / chunk); sigmoid_bias (float32 [heads]): the weight of a visible
+    key is sigmoid(score + bias[h]) and nothing is normalised."""
+    for t in (sink_values, sigmoid_bias):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert token_entry.dtype == torch.int32 and positions.dtype == torch.int32
@@ -526,7 +777,8 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.T
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(token_entry), _ptr(positions), c_int(n_tokens),
         c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(value_dim or head_dim), c_int(k_pages.shape[2]), c_int(window or 0),
-        c_int(keep_first or 0), c_float(scale), c_float(softcap or 0.0), c_int(int(bool(sink))), c_int(_kind(q.dtype)), _stream()))
+        c_int(keep_first or 0), c_float(scale), c_float(softcap or 0.0), c_int(int(bool(sink))), c_int(_kind(q.dtype)), _stream(),
+        _ptr(sink_values), c_int(chunk or 0), _ptr(sigmoid_bias)))
 
 
 def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, n: int) -> None:
@@ -580,7 +832,7 @@ def decode_splits(n_entries: int, n_kv: int, max_keys: int, sms: int = 0) -> int
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
                            n_kv: int, head_dim: int, window: int, scale: float, splits=None, max_keys: int = 0,
-                           softcap: float = 0.0, sink: bool = False, keep_first: int = 0) -> None:
+                           softcap: float = 0.0, sink: bool = False, keep_first: int = 0, sink_values=None) -> None:
     """One query token per entry (row e of q), attending to its request's kv_lens[e] keys.
     max_keys: an upper bound of kv_lens, if the host knows one below the table's width.
     softcap, sink, keep_first: as in paged_attention_generic (the CUDA-core kernel takes them)."""
@@ -598,13 +850,14 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
             c_void_p(buf.data_ptr()), c_int(_kind(q.dtype)))
     # bfloat16 with a head size of 64 or 128 and pages of a power of two: the query heads of a
     # group as rows of warp-level MMAs (tensor-core library); everything else on the CUDA cores
+    assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads)
     extended = bool(softcap or sink or keep_first)
     if (not extended and q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
             and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
         _check_t(load_tensor().llmk_paged_attention_decode_mma(*args, c_int(max_keys), _stream()))
     else:
         _check(load().llmk_paged_attention_decode(*args, _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
-                                                  c_int(keep_first or 0)))
+                                                  c_int(keep_first or 0), _ptr(sink_values)))
 
 
 def _decode_scratch_floats(n_entries: int, n_heads: int, head_dim: int, splits: int) -> int:
@@ -686,13 +939,22 @@ def attention_tc_take_error() -> int:
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
                     window: int, scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
-                    keep_first: int = 0) -> None:
+                    keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None) -> None:
     """Attention of the step's tokens over their requests' pages; q is the first
     n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: in bfloat16 the
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
     where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
     off the 16-grid among them).  value_dim, softcap, sink, keep_first: see paged_attention_generic, the kernel
-    that takes them in every combination."""
+    that takes them in every combination.  sink_values (a learned score per head for the sink): the general kernel and the
+    split-key decode kernel; chunk and sigmoid_bias (a chunked mask, sigmoid weights): the general kernel, whose one warp
+    per (token, head) walks at most one chunk of keys."""
+    if chunk or sigmoid_bias is not None:
+        paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
+                                ctx.n_tokens, n_heads, n_kv, head_dim, 0 if chunk else window, scale, value_dim=value_dim,
+                                softcap=softcap, chunk=chunk, sigmoid_bias=sigmoid_bias)
+        return
+    if sink_values is not None:
+        sink = True
     extended = bool((value_dim and value_dim != head_dim) or softcap or sink or keep_first)
     if (extended and ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
             and (not value_dim or value_dim == head_dim)):
@@ -705,9 +967,9 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
         splits = max(1, min(16, 2 * decode_splits(ctx.n_entries, n_kv, max_keys), _ceil_div(max_keys, 32)))
         paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries,
                                n_heads, n_kv, head_dim, window, scale, splits=splits, max_keys=max_keys,
-                               softcap=softcap, sink=sink, keep_first=keep_first)
+                               softcap=softcap, sink=sink, keep_first=keep_first, sink_values=sink_values)
         return
-    if (extended and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
+    if (extended and sink_values is None and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
             and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):
         attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
                      ctx.n_entries, n_heads, n_kv, head_dim, window, scale, softcap=softcap, sink=sink, keep_first=keep_first)
@@ -715,7 +977,7 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     if extended:
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                                 ctx.n_tokens, n_heads, n_kv, head_dim, window, scale, value_dim=value_dim,
-                                softcap=softcap, sink=sink, keep_first=keep_first)
+                                softcap=softcap, sink=sink, keep_first=keep_first, sink_values=sink_values)
         return
     if ctx.decode_only and qkv.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256:
         max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])

@@ -171,6 +171,76 @@ rope_pairs_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restr
   }
 }
 
+
+// ---- norm over the whole projection, rotation by computed angles, store ----------------------------------------
+// One CTA per token: sums the split-K partial results, takes the RMS norm of the token's whole q projection
+// (n_heads * dim numbers at once, weights q_gain) and of its whole k projection (n_kv * dim, weights k_gain) before they
+// are split into heads (either gain null: that side is not normed), turns the first 2 * rot_pairs channels of every q and k
+// head by position * freqs[i], channel i against channel i + rot_pairs (halves) or 2i against 2i + 1 (neighbours), and
+// stores k and v at the token's slot.  The row is held in shared memory as float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restrict__ q_out, long long q_out_stride,
+                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                          const float* __restrict__ freqs, int rot_pairs, int halves, const int* __restrict__ positions,
+                          const int* __restrict__ slot_map, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                          int n_heads, int n_kv, int dim, int vdim, int page_size) {
+  extern __shared__ float row_s[];            // [(n_heads + n_kv) * dim]
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  const size_t row = (size_t)t * src_stride;
+  const int qn = n_heads * dim, kn = n_kv * dim;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < qn + kn; c += blockDim.x) {
+    const float v = src.at(row + c);
+    row_s[c] = v;
+    if (c < qn) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+  }
+  const float tq = block_sum(sq, red);
+  const float tk = block_sum(sk, red);
+  const float rq = q_gain ? 1.f / sqrtf(tq / (float)qn + eps) : 1.f;
+  const float rk = (k_gain && kn) ? 1.f / sqrtf(tk / (float)kn + eps) : 1.f;
+  size_t k_base = 0, v_base = 0;
+  if (n_kv) {
+    const int slot = slot_map[t];
+    const size_t page = slot / page_size, off = slot % page_size;
+    k_base = (page * n_kv * page_size + off) * dim;
+    v_base = (page * n_kv * page_size + off) * vdim;
+  }
+  T* q_row = q_out + (size_t)t * q_out_stride;
+  // every channel belongs to one item: a turning pair (two channels) or a channel that passes
+  const int per_head = dim - rot_pairs;       // rot_pairs pairs + (dim - 2 rot_pairs) single channels
+  for (int idx = threadIdx.x; idx < (n_heads + n_kv) * per_head; idx += blockDim.x) {
+    const int head = idx / per_head, i = idx % per_head;
+    const bool is_q = head < n_heads;
+    const float r = is_q ? rq : rk;
+    const float* gain = is_q ? q_gain : k_gain;
+    const int c_base = head * dim;             // column of the head in the row (q heads first, then k heads)
+    const int g_base = is_q ? c_base : c_base - qn;
+    T* dst = is_q ? q_row + (size_t)head * dim : k_pages + k_base + (size_t)(head - n_heads) * page_size * dim;
+    if (i < rot_pairs) {
+      const int d0 = halves ? i : 2 * i, d1 = halves ? i + rot_pairs : 2 * i + 1;
+      const float a = row_s[c_base + d0] * r * (gain ? gain[g_base + d0] : 1.f);
+      const float b = row_s[c_base + d1] * r * (gain ? gain[g_base + d1] : 1.f);
+      float sn, cs;
+      sincosf(pos * freqs[i], &sn, &cs);
+      dst[d0] = from_f32<T>(a * cs - b * sn);
+      dst[d1] = from_f32<T>(b * cs + a * sn);
+    } else {
+      const int d = i + rot_pairs;
+      dst[d] = from_f32<T>(row_s[c_base + d] * r * (gain ? gain[g_base + d] : 1.f));
+    }
+  }
+  const size_t v = row + (size_t)(qn + kn);
+  for (int idx = threadIdx.x; idx < n_kv * vdim; idx += blockDim.x) {
+    const int g = idx / vdim, d = idx % vdim;
+    v_pages[v_base + (size_t)g * page_size * vdim + d] = from_f32<T>(src.at(v + idx));
+  }
+}
+
 }  // namespace
 
 // qkv / partials as in llmk_rope_kv_write; q_out may be the source itself (a pair is read and written by
@@ -192,5 +262,30 @@ LLMK_API int llmk_rope_pairs_kv_write(const void* qkv, const float* partials, in
                   q_out_stride, freqs, rot_pairs, positions, slot_map, (T*)k_pages, (T*)v_pages, n_heads, n_kv, dim,
                   vdim, page_size);
     LLMK_LAUNCH_CHECK("rope_pairs_kv_write");
+  });
+}
+
+// As llmk_rope_pairs_kv_write, with the RMS norm of the whole q and k projections first (gains float32 [n_heads * dim] and
+// [n_kv * dim], each may be null) and the choice of the pairs: halves != 0 turns channel i against i + rot_pairs.
+LLMK_API int llmk_norm_rope_kv_write(const void* qkv, const float* partials, int splits, long long split_stride,
+                                     long long src_stride, void* q_out, long long q_out_stride, const float* q_gain,
+                                     const float* k_gain, float eps, const float* freqs, int rot_pairs, int halves,
+                                     const int* positions, const int* slot_map, void* k_pages, void* v_pages, int n_tokens,
+                                     int n_heads, int n_kv, int dim, int vdim, int page_size, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE((qkv != nullptr) != (partials != nullptr), "norm_rope_kv_write: give qkv or partials");
+  LLMK_REQUIRE(rot_pairs >= 0 && 2 * rot_pairs <= dim, "norm_rope_kv_write: %d pairs do not fit a head of %d", rot_pairs, dim);
+  LLMK_REQUIRE(rot_pairs == 0 || freqs != nullptr, "norm_rope_kv_write: frequencies are missing");
+  const size_t smem = (size_t)(n_heads + n_kv) * dim * sizeof(float);
+  LLMK_REQUIRE(smem <= 200 * 1024, "norm_rope_kv_write: a projection of %d numbers does not fit shared memory", (n_heads + n_kv) * dim);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> src{(const T*)qkv, partials, splits, split_stride};
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_rope_kv_write_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(norm_rope_kv_write_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, src, src_stride, (T*)q_out,
+                  q_out_stride, q_gain, k_gain, eps, freqs, rot_pairs, halves, positions, slot_map, (T*)k_pages, (T*)v_pages,
+                  n_heads, n_kv, dim, vdim, page_size);
+    LLMK_LAUNCH_CHECK("norm_rope_kv_write");
   });
 }

@@ -327,14 +327,15 @@ LLMK_API int llmk_add_dyt(float* resid, const void* delta, const float* partials
 
 // ---- element-wise activations -------------------------------------------------
 // out = act(in), float32 arithmetic; in a tensor or the partial results of a split-K product.
-// kind 0: relu(z)^2; 1: gelu with erf; 2: gelu with tanh; 3: z * sigmoid(z).
-enum : int { LLMK_ACT_RELU2 = 0, LLMK_ACT_GELU_ERF = 1, LLMK_ACT_GELU_TANH = 2, LLMK_ACT_SILU = 3 };
+// kind 0: relu(z)^2; 1: gelu with erf; 2: gelu with tanh; 3: z * sigmoid(z); 4: tanh(z).
+enum : int { LLMK_ACT_RELU2 = 0, LLMK_ACT_GELU_ERF = 1, LLMK_ACT_GELU_TANH = 2, LLMK_ACT_SILU = 3, LLMK_ACT_TANH = 4 };
 
 __device__ __forceinline__ float apply_act(float z, int kind) {
   switch (kind) {
     case LLMK_ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
     case LLMK_ACT_GELU_ERF: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
     case LLMK_ACT_GELU_TANH: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    case LLMK_ACT_TANH: return tanhf(z);
     default: return z / (1.f + expf(-z));
   }
 }
@@ -364,7 +365,7 @@ LLMK_API int llmk_act_rows(void* out, const void* in, const float* partials, int
                            long long total, int kind, int dtype, cudaStream_t stream) {
   if (total <= 0) return 0;
   LLMK_REQUIRE((in != nullptr) != (partials != nullptr), "act_rows: give in or partials");
-  LLMK_REQUIRE(kind >= 0 && kind <= 3, "act_rows: unknown activation %d", kind);
+  LLMK_REQUIRE(kind >= 0 && kind <= 4, "act_rows: unknown activation %d", kind);
   size_t blocks = ((size_t)total + 255) / 256;
   if (blocks > (size_t)llmk_sm_count() * 32) blocks = (size_t)llmk_sm_count() * 32;
   return dispatch_dtype(dtype, [&](auto* tag) {
@@ -648,5 +649,39 @@ LLMK_API int llmk_head_rmsnorm_gate(void* out, const float* x, const float* w, c
     launch_kernel(head_rmsnorm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, x, w,
                   (const T*)gate, gate_stride, items, heads, vdim, eps);
     LLMK_LAUNCH_CHECK("head_rmsnorm_gate");
+  });
+}
+
+// ---- clamped gated unit ---------------------------------------------------------------
+// out = g * sigmoid(alpha g) * (u + 1) with g = min(gate + b_g, limit), u = clamp(up + b_u, -limit, limit); in holds
+// [gate | up] per row (a tensor or split-K partial results), bias float32 [2 * inter] or null.  float32 arithmetic.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, MaybePartial<T> in, const float* __restrict__ bias, int inter,
+                                   float limit, float alpha, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / inter, c = i % inter;
+    float g = in.at(r * 2 * inter + c), u = in.at(r * 2 * inter + inter + c);
+    if (bias) { g += bias[c]; u += bias[inter + c]; }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+LLMK_API int llmk_clamped_glu(void* out, const void* gate_up, const float* partials, int splits, long long split_stride,
+                              const float* bias, int rows, int inter, float limit, float alpha, int dtype, cudaStream_t stream) {
+  const long long total = (long long)rows * inter;
+  if (total == 0) return 0;
+  LLMK_REQUIRE((gate_up != nullptr) != (partials != nullptr), "clamped_glu: give gate_up or partials");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> x{(const T*)gate_up, partials, splits, split_stride};
+    long long blocks = (total + 255) / 256;
+    if (blocks > 65535 * 16) blocks = 65535 * 16;
+    launch_kernel(clamped_glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, x, bias, inter, limit, alpha,
+                  (size_t)total);
+    LLMK_LAUNCH_CHECK("clamped_glu");
   });
 }

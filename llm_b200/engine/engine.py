@@ -217,7 +217,7 @@ class Engine:
         # word 0: a token id outside the vocabulary; words 1 and 2: a tensor-core product or attention
         # kernel whose bounded wait gave up (the kernels write there while this engine's step runs)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.resid = torch.zeros((self.max_tokens, self.hidden), dtype=torch.float32, device=self.device)
+        self.resid = torch.zeros((self.max_tokens, self.hidden * self.spec.stream_copies), dtype=torch.float32, device=self.device)
         self.workspace = Workspace(self.max_tokens, self.device)
         self._head_rows = None
         self._logits = None

@@ -43,6 +43,7 @@ class ModelSpec:
     final_norm: Optional[PartSpec]    # None: the head takes the stream as it is
     head: PartSpec
     eos_token_id: Optional[int] = None
+    stream_copies: int = 1            # copies of the residual stream a token carries side by side (hyper-connections)
 
     def validate(self) -> None:
         n = len(self.layers)

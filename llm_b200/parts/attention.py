@@ -13,7 +13,11 @@ Further options, each a parameter and off by default: values of another size tha
 score 0 in the softmax's denominator that carries no value, so that a query may attend to
 nothing; first tokens of a request that stay visible after the window has passed them
 (keep_first; their pages are then never given back); a position part that turns neighbouring
-pairs of channels (kind "rope_pairs"); other tensor names.
+pairs of channels (kind "rope_pairs"); other tensor names.  Further: an RMS norm over the token's whole q projection and
+whole k projection, before they are split into heads and before rotation (qk_norm="whole", weights `q.norm`, `k.norm`);
+a mask by chunks (a query sees the keys at or before it whose position has the same floor(position / chunk), chunks
+counted from the request's first token); and sigmoid weights, sigmoid(score + b_h) with a learned number per head and
+no normalisation over the keys (weights="sigmoid").
 """
 from __future__ import annotations
 
@@ -34,7 +38,8 @@ class PagedAttention(Part):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position=None,
                  window=None, scale=None, shares_cache: bool = False, bias: bool = False, value_dim=None, softcap=None,
-                 sink: bool = False, keep_first: int = 0, names=None, prefix: str = "", dtype=None, device=None):
+                 sink: bool = False, keep_first: int = 0, names=None, chunk=None, weights: str = "softmax", qk_norm=None,
+                 norm_eps: float = 1e-6, prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} heads do not divide into {num_kv_heads} kv heads")
@@ -51,10 +56,18 @@ class PagedAttention(Part):
         if self.keep_first and not self.window:
             self.keep_first = 0                   # without a window every token is seen anyway
         self.names = dict(_NAMES, **(names or {}))
+        self.chunk = int(chunk) if chunk else 0
+        if weights not in ("softmax", "sigmoid") or qk_norm not in (None, "whole"):
+            raise ValueError(f"attention: weights '{weights}' or qk_norm '{qk_norm}' is not known")
+        self.sigmoid, self.qk_norm, self.norm_eps = weights == "sigmoid", qk_norm, float(norm_eps)
+        if self.chunk and (self.window or self.keep_first):
+            raise ValueError("attention: a chunked mask takes no window and no kept tokens")
+        if self.sigmoid and (self.sink or self.softcap):
+            raise ValueError("attention: sigmoid weights take no sink and no soft cap")
         # the options above, and pair rotation, run on the path that rotates and stores with one kernel and
         # attends with a kernel that takes them (see forward)
         self.extended = bool(self.value_dim != head_dim or self.softcap or self.sink or self.keep_first
-                             or (self.position is not None and hasattr(self.position, "frequencies")))
+                             or self.chunk or self.sigmoid or self.qk_norm or (self.position is not None and hasattr(self.position, "frequencies")))
         if self.extended and (bias or (self.position is not None and not hasattr(self.position, "frequencies"))):
             raise ValueError("attention: value_dim, softcap, sink and keep_first go with pair rotation or no positions, without biases")
         self.q_size = num_heads * head_dim
@@ -65,6 +78,7 @@ class PagedAttention(Part):
         self.w_o = None
         self.b_qkv = None
         self.b_o = None
+        self.score_bias = self.q_gain = self.k_gain = None
 
     def parameters(self):
         n = lambda k: self.name(self.names[k])
@@ -73,6 +87,12 @@ class PagedAttention(Part):
             p[n("k")] = ParamInfo((self.kv_size, self.hidden_size))
             p[n("v")] = ParamInfo((self.v_size, self.hidden_size))
         p[n("o")] = ParamInfo((self.hidden_size, self.num_heads * self.value_dim))
+        if self.sigmoid:
+            p[self.name(self.names.get("score_bias", "pb"))] = ParamInfo((self.num_heads,), kind="gain", init="normal")
+        if self.qk_norm:
+            p[self.name(self.names.get("q_norm", "q.norm"))] = ParamInfo((self.q_size,), kind="gain", init="ones_normal")
+            if not self.shares_cache:
+                p[self.name(self.names.get("k_norm", "k.norm"))] = ParamInfo((self.kv_size,), kind="gain", init="ones_normal")
         if self.bias:
             p[self.name("q_proj.bias")] = ParamInfo((self.q_size,), kind="gain", init="normal")
             if not self.shares_cache:
@@ -88,6 +108,12 @@ class PagedAttention(Part):
             parts += [n("k"), n("v")]
         self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0].contiguous()
         self.w_o = n("o").contiguous()
+        if self.sigmoid:
+            self.score_bias = tensors[self.name(self.names.get("score_bias", "pb"))].contiguous()
+        if self.qk_norm:
+            self.q_gain = tensors[self.name(self.names.get("q_norm", "q.norm"))].contiguous()
+            if not self.shares_cache:
+                self.k_gain = tensors[self.name(self.names.get("k_norm", "k.norm"))].contiguous()
         if self.bias:
             names = ["q_proj.bias"] + ([] if self.shares_cache else ["k_proj.bias", "v_proj.bias"])
             self.b_qkv = torch.cat([tensors[self.name(n)] for n in names]).contiguous()
@@ -96,6 +122,8 @@ class PagedAttention(Part):
     def cache_need(self):
         if self.shares_cache:
             return None
+        if self.chunk:      # the keys of a query's chunk lie among the last `chunk` tokens: pages behind them go back
+            return CacheNeed("window", self.num_kv_heads, self.head_dim, self.chunk, value_dim=self.value_dim)
         return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window,
                          value_dim=self.value_dim, keep_first=self.keep_first)
 
@@ -180,12 +208,19 @@ class PagedAttention(Part):
         qkv = linear(x, self.w_qkv, ws.get("qkv", T, self.q_size + self.kv_size + self.v_size, self.dtype), T,
                      allow_partial=FUSE_PARTIALS)
         freqs = self.position.frequencies() if self.position is not None else None
-        q = ops.rope_pairs_kv_write(qkv, freqs, ctx.positions, view.group.slot_map, k_pages, v_pages, T, H,
-                                    0 if self.shares_cache else n_kv, D, V,
-                                    q_out=ws.get("q_rot", T, self.q_size, self.dtype) if isinstance(qkv, ops.PartialSum) else None)
+        halves = getattr(self.position, "layout", "pairs") == "halves"
+        q_out = ws.get("q_rot", T, self.q_size, self.dtype) if isinstance(qkv, ops.PartialSum) else None
+        if self.qk_norm or halves:
+            q = ops.norm_rope_kv_write(qkv, self.q_gain, self.k_gain, self.norm_eps, freqs, halves, ctx.positions,
+                                       view.group.slot_map, k_pages, v_pages, T, H, 0 if self.shares_cache else n_kv, D, V,
+                                       q_out=q_out)
+        else:
+            q = ops.rope_pairs_kv_write(qkv, freqs, ctx.positions, view.group.slot_map, k_pages, v_pages, T, H,
+                                        0 if self.shares_cache else n_kv, D, V, q_out=q_out)
         attn = ws.get("attn_out", T, H * V, self.dtype)
         ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, H, n_kv, D, self.window or 0, self.scale,
-                            value_dim=V, softcap=self.softcap, sink=self.sink, keep_first=self.keep_first)
+                            value_dim=V, softcap=self.softcap, sink=self.sink, keep_first=self.keep_first,
+                            chunk=self.chunk, sigmoid_bias=self.score_bias)
         return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 

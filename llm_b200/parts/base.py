@@ -45,7 +45,7 @@ class ParamInfo:
 
     kind: "matrix" is kept in the compute dtype; "gain" is a small vector kept in
     float32; "int_table" is kept as int32.  init names the random-weights rule:
-    "normal" N(0, 0.02), "ones_normal" 1 + N(0, 0.01), "zeros"."""
+    "normal" N(0, 0.02), "ones_normal" 1 + N(0, 0.01), "zeros", "eye_normal" (a matrix: identity + N(0, 0.01))."""
 
     shape: Tuple[int, ...]
     kind: str = "matrix"

@@ -17,10 +17,11 @@ from .linear import linear
 class TokenEmbedding(Part):
     role = "embedding"
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", prefix: str = "", dtype=None,
-                 device=None):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", copies: int = 1, prefix: str = "",
+                 dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.copies = int(copies)             # a stream kept as several copies: each starts as the embedding
         self.weight_name = weight_name        # "": the table is the tensor named like the part
         self.table = None
 
@@ -31,8 +32,11 @@ class TokenEmbedding(Part):
         self.table = tensors[self.name(self.weight_name)].contiguous()
 
     def forward(self, ctx, stream: ResidualStream) -> None:
-        ops.embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, ctx.status)
-        stream.pending = None
+        if self.copies > 1:
+            ops.hc_embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, self.copies, ctx.status)
+        else:
+            ops.embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, ctx.status)
+        stream.pending = stream.pending_post = None
 
 
 class LMHead(Part):
@@ -66,7 +70,12 @@ class LMHead(Part):
         R = ctx.n_logit_rows
         if stream.pending is not None and stream.pending_post is not None:
             stream.fold(ctx)          # a term that is still to be normed cannot be gathered as it is
-        ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
+        copies = stream.resid.shape[1] // self.hidden_size
+        if copies > 1:                # a stream kept as several copies: the model's output is their sum
+            stream.fold(ctx)
+            ops.hc_gather_sum(rows, stream.resid, ctx.logit_rows, R, copies)
+        else:
+            ops.gather_rows(rows, stream.resid, stream.pending, ctx.logit_rows, R)
         if final_norm is not None:
             final_norm.forward_rows(rows, R, normed)
         else:

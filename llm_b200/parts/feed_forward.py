@@ -95,3 +95,51 @@ class ActMLP(Part):
 
 
 register_part("ffn", "mlp", ActMLP)
+
+
+class ClampedGLU(Part):
+    """down( g * sigmoid(alpha g) * (u + 1) ) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit): a gated
+    unit whose gate is cut off above, whose linear branch is cut off on both sides and shifted by one.  All three
+    projections carry biases unless bias is off.  Tensors `<prefix>.gate|up|down` and `<name>.b`; limit and alpha
+    are parameters."""
+
+    role = "ffn"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702, bias: bool = True,
+                 prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if min(hidden_size, intermediate_size) <= 0 or not limit > 0:
+            raise ValueError("clamped gated unit: sizes and limit must be positive")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.alpha, self.bias = float(limit), float(alpha), bool(bias)
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
+
+    def parameters(self):
+        n, W, I = self.name, self.hidden_size, self.intermediate_size
+        p = {n("gate"): ParamInfo((I, W)), n("up"): ParamInfo((I, W)), n("down"): ParamInfo((W, I))}
+        if self.bias:
+            p.update({n("gate.b"): ParamInfo((I,), kind="gain", init="normal"), n("up.b"): ParamInfo((I,), kind="gain", init="normal"),
+                      n("down.b"): ParamInfo((W,), kind="gain", init="normal")})
+        return p
+
+    def bind(self, tensors):
+        t = lambda local: tensors[self.name(local)]
+        self.w_gate_up = torch.cat([t("gate"), t("up")], dim=0).contiguous()
+        self.w_down = t("down").contiguous()
+        if self.bias:
+            self.b_gate_up = torch.cat([t("gate.b"), t("up.b")]).contiguous()
+            self.b_down = t("down.b").contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        I = self.intermediate_size
+        # one product for gate and up; its split-K partial results go unsummed to the activation kernel, which
+        # adds the biases, clamps and multiplies in float32
+        gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * I, self.dtype), T, allow_partial=FUSE_PARTIALS)
+        act = ws.get("ffn_act", T, I, self.dtype)
+        ops.clamped_glu(act, gate_up, self.b_gate_up, T, self.limit, self.alpha)
+        return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS,
+                      bias=self.b_down)
+
+
+register_part("ffn", "clamped_glu", ClampedGLU)

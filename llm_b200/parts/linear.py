@@ -64,6 +64,8 @@ def linear_act(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: i
     dimension): the caller then runs the product and the activation kernel."""
     if rows == 0:
         return True
+    if act not in ops.EPILOGUE_ACTIVATIONS:
+        return False
     if x.dtype != torch.bfloat16 or not ops.gemm_act_available(x, weight, out, rows):
         return False
     ops.gemm_act(x, weight, out, rows, act)

@@ -55,12 +55,16 @@ class PairRotary(Part):
     ({factor, low, high, original}): kept where l < original/high, divided by factor where l > original/low,
     and in between blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  The part
     gives the frequencies (float32, evaluated in float64 and rounded once); the angle is one float32 product in
-    the kernel that rotates and stores, so no table bounds the position."""
+    the kernel that rotates and stores, so no table bounds the position.  layout "halves" pairs channel i with channel
+    i + dims/2 (rotate-half on the first dims channels) with the same frequencies."""
 
     role = "position"
 
-    def __init__(self, dims: int, base: float, scaling=None, prefix: str = "", dtype=None, device=None):
+    def __init__(self, dims: int, base: float, scaling=None, layout: str = "pairs", prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
+        if layout not in ("pairs", "halves"):
+            raise ValueError(f"pair rotation: layout '{layout}' is neither 'pairs' nor 'halves'")
+        self.layout = layout        # "halves": channel i turns against channel i + dims/2 instead of 2i against 2i + 1
         if dims < 0 or dims % 2:
             raise ValueError(f"pair rotation: dims {dims} must be even and not negative")
         self.dims, self.base = int(dims), float(base)

@@ -1,0 +1,272 @@
+"""Recurrent mixers with a matrix state per head and a diagonal decay, and two mixers that are built from other mixers.
+
+  wkv            RWKV-style time mixing: every projection reads its own blend of the token's row and the previous
+                 token's; o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_{t-1} + k_t v_t^T
+  ssd            state-space duality (Mamba-2): a short convolution on x, B, C; S_t = a_t S_{t-1} + dt_t B_t x_t^T,
+                 y_t = S_t^T C_t + D x_t with one decay per head and token
+  conv_input     a wrapper: the inner mixer reads h + conv(h), a short causal convolution per channel
+  parallel       a wrapper: two mixers read the same rows; the result is the mean of their RMS-normed outputs
+
+None of them keeps keys: a request's past is its state slot (float32, zero at admission), read at the start of
+the step's tokens and written back at their end, so a whole prompt, a portion and a decoded token run the same
+recurrence.  A part's state is one flat float32 row per request; a wrapper's row is its own numbers followed by its
+inner parts' (each part gets a column range of the row, starting on a 16-byte boundary).  Decays, their logarithms,
+step sizes, states and the norms are float32; projections and convolutions run in the compute dtype.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ..csrc import ops
+from .base import ParamInfo, Part, StateNeed, build_part, register_part
+from .linear import FUSE_PARTIALS, linear
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+def _state_numel(need) -> int:
+    if need is None:
+        return 0
+    if need.dtype != torch.float32:
+        raise ValueError("a mixer inside another keeps its state in float32")
+    n = 1
+    for s in need.shape:
+        n *= int(s)
+    return n
+
+
+def _sub_view(view, state):
+    """The layer's view as an inner part sees it: the same cache, its own columns of the state row."""
+    return dataclasses.replace(view, state=state)
+
+
+class TimeMixWKV(Part):
+    """Tensors (local names): mu.r|k|v|g|w [W] (blend weights), r, k, v, g [H*D, W], w1 [rank, W], w2 [H*D, rank],
+    w0 [H*D] (decay through a low rank: w = exp(-exp(w2 tanh(w1 x_w) + w0))), u [H, D] (the current token's bonus),
+    norm [H*D], o [W, H*D].  The output of every head is divided by its root mean square, scaled by norm and by
+    silu(g x_g).  State row: [the previous token's input: W | S: H * D * D]."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, eps: float, decay_rank: int = 16, prefix: str = "",
+                 dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if min(hidden_size, num_heads, head_dim, decay_rank) <= 0:
+            raise ValueError("wkv: sizes must be positive")
+        if head_dim > 256:
+            raise ValueError(f"wkv: head size {head_dim} exceeds 256, the most the recurrence kernel takes")
+        self.hidden_size, self.num_heads, self.head_dim = int(hidden_size), int(num_heads), int(head_dim)
+        self.eps, self.decay_rank = float(eps), int(decay_rank)
+        self.inner = self.num_heads * self.head_dim
+        self.shift_cols = _pad4(self.hidden_size)
+        self.mu = self.w_rkvg = self.w1 = self.w2 = self.w0 = self.bonus = self.gain = self.w_o = None
+
+    def parameters(self):
+        n, W, I, R = self.name, self.hidden_size, self.inner, self.decay_rank
+        p = {n("mu." + m): ParamInfo((W,), kind="gain", init="normal") for m in "rkvgw"}
+        p.update({n(m): ParamInfo((I, W)) for m in "rkvg"})
+        p.update({n("w1"): ParamInfo((R, W), free_dims=(0,)), n("w2"): ParamInfo((I, R), free_dims=(1,)),
+                  n("w0"): ParamInfo((I,), kind="gain", init="normal"),
+                  n("u"): ParamInfo((self.num_heads, self.head_dim), kind="gain", init="normal"),
+                  n("norm"): ParamInfo((I,), kind="gain", init="ones_normal"), n("o"): ParamInfo((W, I))})
+        return p
+
+    def bind(self, tensors):
+        t = lambda local: tensors[self.name(local)]
+        if t("w1").shape[0] != t("w2").shape[1]:
+            raise ValueError(f"{self.prefix}: the decay's factors disagree on their rank ({t('w1').shape[0]} and {t('w2').shape[1]})")
+        self.decay_rank = int(t("w1").shape[0])
+        self.mu = torch.stack([t("mu." + m) for m in "rkvgw"]).contiguous()                  # [5, W] float32
+        self.w_rkvg = torch.stack([t(m) for m in "rkvg"]).contiguous()                        # [4, H*D, W]
+        self.w1, self.w2 = t("w1").contiguous(), t("w2").contiguous()
+        self.w0, self.bonus, self.gain = t("w0").contiguous(), t("u").contiguous(), t("norm").contiguous()
+        self.w_o = t("o").contiguous()
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.shift_cols + self.inner * self.head_dim,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        W, I, R = self.hidden_size, self.inner, self.decay_rank
+        shift, S = view.state[:, :self.shift_cols], view.state[:, self.shift_cols:]
+        mixes = ws.get("wkv_mixes", T, 5 * W, self.dtype)
+        ops.token_shift(mixes, x, self.mu, shift, ctx)
+        rkvg = ws.get("wkv_rkvg", T, 4 * I, self.dtype)
+        ops.gemm_heads(mixes[:, :4 * W], self.w_rkvg, rkvg, T, 4)          # four products of four inputs in one launch
+        low = linear(mixes[:, 4 * W:], self.w1, ws.get("wkv_low", T, R, self.dtype), T)
+        low_t = ws.get("wkv_low_t", T, R, self.dtype)
+        ops.act_rows(low_t, low, T, "tanh")
+        # the decay's pre-activation in float32; bias and the two exponentials are the recurrence kernel's
+        z = linear(low_t, self.w2, ws.get("wkv_z", T, I, torch.float32), T)
+        o = ws.get("wkv_o", T, I, torch.float32)
+        ops.wkv_scan(o, rkvg[:, :I], rkvg[:, I:2 * I], rkvg[:, 2 * I:3 * I], z, self.w0, self.bonus, S, ctx,
+                     shift_src=x, shift_state=shift)
+        normed = ws.get("attn_out", T, I, self.dtype)
+        ops.group_rmsnorm_gate(normed, o, self.gain, rkvg[:, 3 * I:], T, self.num_heads, self.eps)
+        return linear(normed, self.w_o, ws.get("mixer_out", T, W, self.dtype), T, allow_partial=FUSE_PARTIALS)
+
+
+register_part("mixer", "wkv", TimeMixWKV)
+
+
+class StateSpaceDuality(Part):
+    """Tensors (local names): in [2 I + 2 G N + H, W] laid out [z: I | x: I | B: G N | C: G N | dt: H] with I = H * V;
+    conv [I + 2 G N, taps] and conv.b (x, B and C pass the convolution and silu); dt_bias, A_log, D [H];
+    norm [I]; o [W, I].  y * silu(z) is RMS-normed in norm_groups equal parts (the gate comes before the norm).
+    State row: [the convolution's last taps - 1 inputs | S: H * N * V]."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, num_heads: int, value_dim: int, state_size: int, groups: int, norm_groups: int,
+                 taps: int, eps: float, prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if min(hidden_size, num_heads, value_dim, state_size, groups, norm_groups, taps) <= 0:
+            raise ValueError("ssd: sizes must be positive")
+        if num_heads % groups or (num_heads * value_dim) % norm_groups:
+            raise ValueError(f"ssd: {num_heads} heads of {value_dim} do not divide into {groups} groups or {norm_groups} norm groups")
+        if state_size > 256:
+            raise ValueError(f"ssd: state size {state_size} exceeds 256, the most the recurrence kernel takes")
+        self.hidden_size, self.num_heads, self.value_dim, self.state_size = hidden_size, num_heads, value_dim, state_size
+        self.groups, self.norm_groups, self.taps, self.eps = groups, norm_groups, taps, float(eps)
+        self.inner = num_heads * value_dim
+        self.conv_channels = self.inner + 2 * groups * state_size
+        self.conv_cols = _pad4((taps - 1) * self.conv_channels)
+        self.w_in = self.w_conv = self.b_conv = self.dt_bias = self.a_log = self.skip = self.gain = self.w_o = None
+
+    def parameters(self):
+        n, W, I, H, C = self.name, self.hidden_size, self.inner, self.num_heads, self.conv_channels
+        return {n("in"): ParamInfo((I + C + H, W)), n("conv"): ParamInfo((C, self.taps), kind="gain", init="normal"),
+                n("conv.b"): ParamInfo((C,), kind="gain", init="normal"), n("dt_bias"): ParamInfo((H,), kind="gain", init="normal"),
+                n("A_log"): ParamInfo((H,), kind="gain", init="normal"), n("D"): ParamInfo((H,), kind="gain", init="ones_normal"),
+                n("norm"): ParamInfo((I,), kind="gain", init="ones_normal"), n("o"): ParamInfo((W, I))}
+
+    def bind(self, tensors):
+        t = lambda local: tensors[self.name(local)].contiguous()
+        self.w_in, self.w_conv, self.b_conv = t("in"), t("conv"), t("conv.b")
+        self.dt_bias, self.a_log, self.skip, self.gain, self.w_o = t("dt_bias"), t("A_log"), t("D"), t("norm"), t("o")
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.conv_cols + self.num_heads * self.state_size * self.value_dim,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        I, C, H, GN = self.inner, self.conv_channels, self.num_heads, self.groups * self.state_size
+        conv_state, S = view.state[:, :self.conv_cols], view.state[:, self.conv_cols:]
+        proj = linear(x, self.w_in, ws.get("ssd_in", T, I + C + H, self.dtype), T)
+        xbc = ws.get("ssd_xbc", T, C, self.dtype)
+        ops.short_conv(xbc, proj[:, I:I + C], self.w_conv, self.b_conv, conv_state, ctx, silu=True)
+        y = ws.get("ssd_y", T, I, torch.float32)
+        ops.ssd_scan(y, xbc[:, :I], xbc[:, I:I + GN], xbc[:, I + GN:], proj[:, I + C:], self.dt_bias, self.a_log, self.skip,
+                     S, ctx, H, self.groups, self.state_size, self.value_dim)
+        normed = ws.get("ssd_normed", T, I, self.dtype)
+        ops.group_rmsnorm_gate(normed, y, self.gain, proj[:, :I], T, self.norm_groups, self.eps, gate_first=True)
+        return linear(normed, self.w_o, ws.get("ssd_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+
+
+register_part("mixer", "ssd", StateSpaceDuality)
+
+
+class ConvInput(Part):
+    """The inner mixer reads h + conv(h): conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) per channel, zeros before the
+    request's first token, no bias.  Tensor `<prefix>.<weight_name>` [W, taps].  State row: [the last taps - 1
+    inputs | the inner mixer's]; the inner mixer's cache is the layer's."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, taps: int, inner, weight_name: str = "conv", prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if hidden_size <= 0 or not (1 <= taps <= 16):
+            raise ValueError(f"input convolution: width {hidden_size} must be positive and taps {taps} 1 to 16")
+        self.hidden_size, self.taps, self.weight_name = int(hidden_size), int(taps), weight_name
+        self.inner = build_part("mixer", inner, dtype, device)
+        self.own_cols = _pad4((self.taps - 1) * self.hidden_size)
+        self.inner_cols = _state_numel(self.inner.state_need())
+        self.w = None
+
+    def children(self):
+        return [self.inner]
+
+    def parameters(self):
+        return {self.name(self.weight_name): ParamInfo((self.hidden_size, self.taps), kind="gain", init="normal")}
+
+    def bind(self, tensors):
+        self.w = tensors[self.name(self.weight_name)].contiguous()
+
+    def cache_need(self):
+        return self.inner.cache_need()
+
+    def state_need(self):
+        return StateNeed((max(self.own_cols + self.inner_cols, 4),), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        out = ctx.workspace.get("conv_input", ctx.n_tokens, self.hidden_size, self.dtype)
+        ops.short_conv(out, x, self.w, None, view.state[:, :self.own_cols], ctx, residual=True)
+        inner_state = view.state[:, self.own_cols:] if self.inner_cols else None
+        return self.inner.forward(out, ctx, _sub_view(view, inner_state))
+
+
+register_part("mixer", "conv_input", ConvInput)
+
+
+class ParallelMixers(Part):
+    """out = (rms(left(h)) * g_l + rms(right(h)) * g_r) / 2, each RMS norm over the model width with a plain weight
+    (`<prefix>.<left_name>`, `<prefix>.<right_name>`).  At most one side keeps keys (the layer has one cache); the
+    state row is the left side's followed by the right side's."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, left, right, eps: float, left_name: str = "left.out", right_name: str = "right.out",
+                 prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        self.hidden_size, self.eps = int(hidden_size), float(eps)
+        self.left_name, self.right_name = left_name, right_name
+        self.left, self.right = build_part("mixer", left, dtype, device), build_part("mixer", right, dtype, device)
+        if self.left.cache_need() is not None and self.right.cache_need() is not None:
+            raise ValueError("parallel mixers: only one side may keep keys and values")
+        self.left_cols = _pad4(_state_numel(self.left.state_need()))
+        self.right_cols = _state_numel(self.right.state_need())
+        self.g_left = self.g_right = None
+
+    def children(self):
+        return [self.left, self.right]
+
+    def parameters(self):
+        W = self.hidden_size
+        return {self.name(self.left_name): ParamInfo((W,), kind="gain", init="ones_normal"),
+                self.name(self.right_name): ParamInfo((W,), kind="gain", init="ones_normal")}
+
+    def bind(self, tensors):
+        self.g_left = tensors[self.name(self.left_name)].contiguous()
+        self.g_right = tensors[self.name(self.right_name)].contiguous()
+
+    def cache_need(self):
+        return self.left.cache_need() or self.right.cache_need()
+
+    def state_need(self):
+        n = self.left_cols + self.right_cols
+        return StateNeed((n,), torch.float32) if n else None
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        ls = view.state[:, :self.left_cols] if self.left_cols else None
+        rs = view.state[:, self.left_cols:] if self.right_cols else None
+        a = self.left.forward(x, ctx, _sub_view(view, ls))
+        # unsummed partial results live until the next product: the left side's are summed before the right side runs
+        a = ops.settle(a, ws.get("parallel_left", T, self.hidden_size, self.dtype), T)
+        b = self.right.forward(x, ctx, _sub_view(view, rs))
+        out = ws.get("parallel_out", T, self.hidden_size, self.dtype)
+        ops.pair_norm_mean(out, a, b, self.g_left, self.g_right, T, self.eps)
+        return out
+
+
+register_part("mixer", "parallel", ParallelMixers)

@@ -173,6 +173,8 @@ def random_tensor(name: str, info: ParamInfo, seed: int) -> torch.Tensor:
         return 1.0 + x * 0.01
     if info.init == "zeros":
         return torch.zeros(info.shape, dtype=torch.float32)
+    if info.init == "eye_normal":        # a square matrix near the identity
+        return torch.eye(info.shape[0], info.shape[1], dtype=torch.float32) + x * 0.01
     raise ValueError(f"unknown init rule '{info.init}'")
 
 
