@@ -90,6 +90,19 @@ def streams_write(xs, mix, w_out, y):
 
 
 # ---- mixer: wkv --------------------------------------------------------------------------------------------
+def wkv_recurrence(r, k, v, decay, bonus, state=None):
+    """o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, then S_t = diag(w_t) S_(t-1) + k_t v_t^T.  r, k, v, decay [T, H, D];
+    bonus [H, D]; state [H, D, D] (key channel, value channel) or None for zeros.  Returns (o [T, H, D], last state)."""
+    T, H, D = r.shape
+    state = r.new_zeros(H, D, D) if state is None else state.clone()
+    o = r.new_zeros(T, H, D)
+    for t in range(T):
+        kv = k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hi,hij->hj", r[t], state + bonus[:, :, None] * kv)
+        state = decay[t][:, :, None] * state + kv
+    return o, state
+
+
 def wkv_mixer(h, p, m, eps):
     """RWKV-style time mixing.  p: the mixer's tensors by their local names; m: its sizes."""
     T, W = h.shape
@@ -101,18 +114,25 @@ def wkv_mixer(h, p, m, eps):
     v = (lerp("v") @ p["v"].T).view(T, H, D)
     gate = silu(lerp("g") @ p["g"].T)
     decay = torch.exp(-torch.exp(torch.tanh(lerp("w") @ p["w1"].T) @ p["w2"].T + p["w0"])).view(T, H, D)
-    bonus = p["u"]                                                 # [H, D]
-    state = h.new_zeros(H, D, D)                                   # [head, key channel, value channel]
-    o = h.new_zeros(T, H, D)
-    for t in range(T):
-        kv = k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hi,hij->hj", r[t], state + bonus[:, :, None] * kv)
-        state = decay[t][:, :, None] * state + kv
+    o, _ = wkv_recurrence(r, k, v, decay, p["u"])
     o = rms_unit(o, eps).reshape(T, H * D) * p["norm"] * gate
     return o @ p["o"].T
 
 
 # ---- mixer: latent attention -------------------------------------------------------------------------------
+def window_sink_softmax(score, size, sink, v, positions=None, key_positions=None):
+    """Softmax over the keys j with 0 <= i - j < size, whose denominator also holds exp(sink_h).  score [H, Tq, Tk]
+    (already scaled), sink [H], v [Tk, H, V]; positions of queries and keys default to 0, 1, ...  Returns [Tq, H, V]."""
+    i = (torch.arange(score.shape[1]) if positions is None else positions)[:, None]
+    j = (torch.arange(score.shape[2]) if key_positions is None else key_positions)[None, :]
+    seen = (i - j >= 0) & (i - j < size)
+    score = score.masked_fill(~seen, -math.inf)
+    top = torch.maximum(score.max(dim=-1).values, sink[:, None])                           # [H, Tq]
+    e = torch.exp(score - top[..., None])
+    weights = e / (e.sum(dim=-1) + torch.exp(sink[:, None] - top))[..., None]
+    return torch.einsum("hij,jhv->ihv", weights, v)
+
+
 def latent_attention_mixer(h, p, m, eps):
     T, W = h.shape
     H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
@@ -126,17 +146,21 @@ def latent_attention_mixer(h, p, m, eps):
     k_plain = (c @ p["uk"].T).view(T, H, D)
     v = (c @ p["uv"].T).view(T, H, V)
     score = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihr,jr->hij", q_rot, k_rot)) * m["scale"]
-    i, j = pos[:, None], pos[None, :]
-    seen = (i - j >= 0) & (i - j < m["mask"]["size"])
-    score = score.masked_fill(~seen, -math.inf)
-    top = torch.maximum(score.max(dim=-1).values, p["sink"][:, None])                      # [H, T]
-    e = torch.exp(score - top[..., None])
-    weights = e / (e.sum(dim=-1) + torch.exp(p["sink"][:, None] - top))[..., None]
-    o = torch.einsum("hij,jhv->ihv", weights, v).reshape(T, H * V)
+    o = window_sink_softmax(score, m["mask"]["size"], p["sink"], v).reshape(T, H * V)
     return o @ p["o"].T
 
 
 # ---- mixer: parallel (chunked sigmoid attention beside a state-space layer) ------------------------------------
+def chunk_sigmoid_weights(score, size, bias, v):
+    """Weights sigmoid(score + bias_h) on the keys j <= i of the query's chunk (floor(i / size) = floor(j / size)), not
+    normalised.  score [H, T, T] (already scaled), bias [H], v [T, H, V] (per query head).  Returns [T, H, V]."""
+    pos = torch.arange(score.shape[1])
+    i, j = pos[:, None], pos[None, :]
+    seen = (j <= i) & (i // size == j // size)
+    weights = torch.sigmoid(score + bias[:, None, None]) * seen
+    return torch.einsum("hij,jhv->ihv", weights, v)
+
+
 def chunked_sigmoid_attention(h, p, m, eps):
     T, W = h.shape
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -148,12 +172,22 @@ def chunked_sigmoid_attention(h, p, m, eps):
     k = rotate_halves(k, pos, m["rot"]["dims"], m["rot"]["base"])
     group = torch.arange(H) // (H // G)
     score = torch.einsum("ihd,jhd->hij", q, k[:, group]) * m["scale"]
-    i, j = pos[:, None], pos[None, :]
-    size = m["mask"]["size"]
-    seen = (j <= i) & (i // size == j // size)
-    weights = torch.sigmoid(score + p["pb"][:, None, None]) * seen
-    o = torch.einsum("hij,jhv->ihv", weights, v[:, group]).reshape(T, H * V)
+    o = chunk_sigmoid_weights(score, m["mask"]["size"], p["pb"], v[:, group]).reshape(T, H * V)
     return o @ p["o"].T
+
+
+def ssd_recurrence(x, B, C, dt, decay, skip, state=None):
+    """S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t.  x [T, H, V]; B, C [T, G, N] (head h uses group
+    h // (H / G)); dt, decay [T, H]; skip [H]; state [H, N, V] or None for zeros.  Returns (y [T, H, V], last state)."""
+    T, H, V = x.shape
+    G, N = B.shape[1], B.shape[2]
+    group = torch.arange(H) // (H // G)
+    state = x.new_zeros(H, N, V) if state is None else state.clone()
+    y = x.new_zeros(T, H, V)
+    for t in range(T):
+        state = decay[t][:, None, None] * state + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
+        y[t] = torch.einsum("hnv,hn->hv", state, C[t][group]) + skip[:, None] * x[t]
+    return y, state
 
 
 def state_space_mixer(h, p, m, eps):
@@ -168,12 +202,7 @@ def state_space_mixer(h, p, m, eps):
     C = xbc[:, inner + G * N:].view(T, G, N)
     dt = softplus(dt + p["dt_bias"])                                # [T, H]
     decay = torch.exp(-torch.exp(p["A_log"]) * dt)
-    group = torch.arange(H) // (H // G)
-    state = h.new_zeros(H, N, V)
-    y = h.new_zeros(T, H, V)
-    for t in range(T):
-        state = decay[t][:, None, None] * state + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
-        y[t] = torch.einsum("hnv,hn->hv", state, C[t][group]) + p["D"][:, None] * x[t]
+    y, _ = ssd_recurrence(x, B, C, dt, decay, p["D"])
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms_unit(y.view(T, parts, inner // parts), eps).reshape(T, inner) * p["norm"]
