@@ -423,8 +423,38 @@ FOPIVIK_SIZES = {
 }
 
 
+def norusun_config(width, pattern, repeats, wkv_heads, heads, kv_heads, dim, kv_rank, rot_dim, q_rank, window, chunk, ssd_heads,
+                   ssd_vdim, state, groups, ff, vocab=32000):
+    """Layers follow `pattern` (w: wkv, l: latent attention with a window and a sink, p: chunked sigmoid attention beside a
+    state-space layer) `repeats` times, each with a clamped gated feed-forward, on four streams."""
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    kinds = {
+        "w": ("wkv", {"heads": wkv_heads, "dim": 64}),
+        "l": ("latent_attention", {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "q_rank": q_rank,
+                                   "scale": (dim + rot_dim) ** -0.5, "mask": {"size": window}, "rot": {"dims": rot_dim, "base": 5e5}}),
+        "p": ("parallel", {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                    "mask": {"size": chunk}, "rot": {"dims": dim, "base": 1e4}},
+                           "right": {"heads": ssd_heads, "vdim": ssd_vdim, "state": state, "groups": groups, "norm_groups": groups,
+                                     "conv": 4}}),
+    }
+    ls = [{"type": kinds[c][0], "mixer": kinds[c][1], "mlp": mlp} for c in pattern * repeats]
+    return {"architecture": "Norusun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "streams": 4, "canon": {"taps": 4},
+            "layers": ls, "max_position": 4096}
+
+
+# name -> (Norusun config, Llama config of the same width, depth, heads and feed-forward size)
+NORUSUN_SIZES = {
+    "2048": (norusun_config(2048, "wllp", 2, 32, 16, 4, 128, 80, 48, 768, 1024, 256, 32, 64, 128, 4, 5632),
+             llama_config(2048, 8, 16, 4, 128, 5632)),
+    "4096": (norusun_config(4096, "wlpl", 1, 64, 32, 8, 128, 80, 48, 1536, 1024, 256, 64, 64, 128, 8, 11008),
+             llama_config(4096, 4, 32, 8, 128, 11008)),
+    "1024-head64": (norusun_config(1024, "wllp", 2, 16, 16, 4, 64, 80, 48, 384, 512, 128, 16, 64, 64, 2, 2816),
+                    llama_config(1024, 8, 16, 4, 64, 2816)),
+}
+
+
 def design_comparison(args, peaks, design: str = "tevudra") -> int:
-    """Prefill and decode throughput of a design (Tevudra or Fopivik) beside Llama at equal layer sizes (random weights,
+    """Prefill and decode throughput of a design (Tevudra, Fopivik or Norusun) beside Llama at equal layer sizes (random weights,
     bfloat16), with the device time of every kernel of one prompt step and one decode step.  One JSON line per size."""
     import collections
 
@@ -513,7 +543,7 @@ def design_comparison(args, peaks, design: str = "tevudra") -> int:
         torch.cuda.empty_cache()
         return out
 
-    table = FOPIVIK_SIZES if design == "fopivik" else DESIGN_SIZES
+    table = {"fopivik": FOPIVIK_SIZES, "norusun": NORUSUN_SIZES}.get(design, DESIGN_SIZES)
     sizes = [s for s in table if not args.sizes or s in args.sizes.split(",")]
     for name in sizes:
         tev, lla = table[name]
@@ -538,14 +568,14 @@ def main() -> int:
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
     ap.add_argument("--mode", default="all",
-                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra", "fopivik"],
+                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra", "fopivik", "norusun"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
                          "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph; "
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
                          "(--batch with --ctx: that one case); "
-                         "tevudra, fopivik: that design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
+                         "tevudra, fopivik, norusun: that design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
     ap.add_argument("--latent", action="store_true", help="decode_attention: the key pages are the value pages too")
-    ap.add_argument("--sizes", default="", help="tevudra, fopivik: which of the sizes to run (comma-separated; default all)")
+    ap.add_argument("--sizes", default="", help="tevudra, fopivik, norusun: which of the sizes to run (comma-separated; default all)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="timeline_prefill: tokens of the prompt step")
     ap.add_argument("--heads", default="32,4,64", help="decode_attention: query heads, kv heads, head size")
@@ -568,7 +598,7 @@ def main() -> int:
     peaks = load_peaks()
     if args.mode == "decode_attention":
         return decode_attention_sweep(args, peaks, torch, ops)
-    if args.mode in ("tevudra", "fopivik"):
+    if args.mode in ("tevudra", "fopivik", "norusun"):
         return design_comparison(args, peaks, args.mode)
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     if args.mode != "all":

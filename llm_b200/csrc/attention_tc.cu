@@ -28,7 +28,14 @@
 // hardware's tanh.approx.f32 (relative error about 2^-11, well inside what the bfloat16 rounding of q, k and P
 // does to a score).  A sink: the row's softmax starts with one term of score 0 and no value (reference 0, sum 1).
 // And, with a window, the request's first keep_first keys: the blocks that hold them are walked before the
-// window's blocks, and the mask lets them through.
+// window's blocks, and the mask lets them through.  The sink's score may be a learned number per head (head_values; it
+// is not scaled): the row then starts at that reference with sum 1.  And the mask may be by chunks instead of a window
+// (chunk > 0): a row at position p sees the keys floor(p / chunk) * chunk .. p, and the tile walks the blocks from the
+// chunk of its first row on.
+//
+// The SIG instantiation has no softmax: the weight of a visible key is sigmoid(score * scale + head_values[head]), computed
+// in float32 as 1 / (1 + exp2(-x log2 e)) and rounded to bfloat16 for the second product like the softmax's P; there is no
+// maximum, no sum, nothing to rescale and no division at the end.  It takes the chunked mask or the plain causal one.
 #include <mutex>
 #include <unordered_map>
 
@@ -116,14 +123,17 @@ struct Smem {
   static constexpr int TOTAL = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256 /* barriers */;
 };
 
-template <int HS, bool EXT>
+enum : int { MODE_PLAIN = 0, MODE_EXT = 1, MODE_SIG = 2 };
+
+template <int HS, int MODE>
 __global__ void __launch_bounds__(THREADS, HS == 64 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long long out_stride,
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_tokens,
                     const int* __restrict__ kv_lens, int n_entries, int n_heads, int n_kv, int page_size, int n_pages,
                     int window, float scale_log2e, int* __restrict__ err_flag, float cap_c1, float cap_c2, int sink,
-                    int keep_first) {
+                    int keep_first, const float* __restrict__ head_values, int chunk) {
+  constexpr bool EXT = MODE == MODE_EXT, SIG = MODE == MODE_SIG;
   // cap_c1 = scale / cap and cap_c2 = cap * log2(e) (both 0 without a cap): a score s becomes tanh(s * c1) * c2
   using S = Smem<HS>;
   constexpr int KB = S::KB;
@@ -200,7 +210,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (entry >= 0) {
     const int p_last = p0 + nt - 1;
-    const int lo_tile = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;   // lowest key any row sees
+    const bool chunked = MODE != MODE_PLAIN && chunk > 0;
+    const int lo_tile = chunked ? (p0 / chunk) * chunk
+                                : (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;      // lowest key any row sees
+    const int lo_last = chunked ? (p_last / chunk) * chunk : (window > 0 ? p_last - window + 1 : 0);   // ... the last row sees
     const int kb_first = lo_tile / BKV, kb_last = p_last / BKV;
     // blocks of kept keys that lie wholly before the window's first block come first
     const int n_keep = (EXT && window > 0 && keep_first > 0) ? min((keep_first + BKV - 1) / BKV, kb_first) : 0;
@@ -304,10 +317,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int tok = r / group, head = r % group;
       const bool row_ok = tok < nt;
       const int pos = p0 + tok;
-      const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+      const int lo = chunked ? (pos / chunk) * chunk : (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
       // with a sink the row starts with one term of score 0: reference 0, sum 1
-      float m_ref = (EXT && sink) ? 0.f : -INFINITY, l = (EXT && sink) ? 1.f : 0.f;
+      // (or of the head's learned score, which is not scaled)
+      float m_ref = (EXT && sink) ? (head_values ? head_values[g * group + head] * 1.4426950408889634f : 0.f) : -INFINITY;
+      float l = (EXT && sink) ? 1.f : 0.f;
+      const float sig_bias = SIG ? -head_values[g * group + head] * 1.4426950408889634f : 0.f;
       const int keep = EXT ? keep_first : 0;
       const bool capped = EXT && cap_c2 > 0.f;
       bool ok = true;
@@ -324,12 +340,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_arrive(s_free);
         // every row sees every key of the block when the block lies inside all windows and below all diagonals
         const bool full = (key0 + BKV - 1 <= p0) &&
-                          (window <= 0 || key0 >= p_last - window + 1 || (EXT && key0 + BKV - 1 < keep));
+                          ((!chunked && window <= 0) || key0 >= lo_last || (EXT && key0 + BKV - 1 < keep));
         // the row's maximum over the block.  The scale is positive, so it is taken over the raw
         // scores and scaled once.  Four running maxima (and sums below) keep the dependent chains short.
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 2 && !SIG; ++c) {
           if (full) {
 #pragma unroll
             for (int j = 0; j < 64; j += 2)
@@ -355,7 +371,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           l *= alpha;
         }
         bool pv_waited = false;
-        if (i > 0 && __any_sync(0xffffffffu, moved)) {
+        if (!SIG && i > 0 && __any_sync(0xffffffffu, moved)) {
           // O holds blocks 0 .. i-1 once their last product is done; rescale this warp's rows
           if (ok) ok = mbar_wait(pv_full, (i - 1) & 1);
           pv_waited = true;
@@ -371,9 +387,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
           tmem_st_wait();
         }
-        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;   // a row that sees nothing yet
+        const float neg_m = SIG ? sig_bias : m_ref == -INFINITY ? 0.f : -m_ref;   // (a row that sees nothing yet: 0)
         // P = exp2(score * scale - reference) as bfloat16 pairs, in place of the scores
-        const uint64_t scale2 = pack_f32x2(scale_log2e, scale_log2e), neg_m2 = pack_f32x2(neg_m, neg_m);
+        // (sigmoid weights: exp2(-(score * scale + bias) log2 e) first, then 1 / (1 + that))
+        const float sc = SIG ? -scale_log2e : scale_log2e;
+        const uint64_t scale2 = pack_f32x2(sc, sc), neg_m2 = pack_f32x2(neg_m, neg_m);
         const uint64_t c1_2 = pack_f32x2(cap_c1, cap_c1), c2_2 = pack_f32x2(cap_c2, cap_c2), zero2 = 0ull;
         uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};               // four pairs of running sums (0.f, 0.f)
 #pragma unroll
@@ -394,6 +412,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c][2 * j]), __uint_as_float(raw[c][2 * j + 1])), scale2, neg_m2), xa, xb);
             }
             float pa = fast_exp2(xa), pb = fast_exp2(xb);
+            if (SIG) {
+              pa = __frcp_rn(1.f + pa);       // exp2 of a large argument is +inf: the weight is then 0
+              pb = __frcp_rn(1.f + pb);
+            }
             if (!full) {
               const int key = key0 + c * 64 + 2 * j;
               if (key > pos || (key < lo && key >= keep)) pa = 0.f;
@@ -424,7 +446,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (ok) ok = mbar_wait(pv_full, (n_blocks - 1) & 1);
       fence_after_sync();
       if (!ok && lane == 0) atomicExch(err_flag, ERR_S);
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = SIG ? 1.f : l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = out + (size_t)(t0 + tok) * out_stride + (size_t)(g * group + head) * HS;
 #pragma unroll
       for (int c = 0; c < HS; c += 64) {
@@ -527,12 +549,12 @@ int get_map3(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint6
 
 int* g_attn_err = nullptr;
 
-template <int HS, bool EXT>
+template <int HS, int MODE>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, long long out_stride,
            const int* block_table, int table_width, const int* cu_tokens, const int* kv_lens, int n_entries,
            int max_tiles, int n_heads, int n_kv, int page_size, int n_pages, int window, float scale_log2e,
-           cudaStream_t stream, float cap_c1, float cap_c2, int sink, int keep_first) {
-  auto kern = attention_tc_kernel<HS, EXT>;
+           cudaStream_t stream, float cap_c1, float cap_c2, int sink, int keep_first, const float* head_values, int chunk) {
+  auto kern = attention_tc_kernel<HS, MODE>;
   constexpr int smem = Smem<HS>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -543,7 +565,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   dim3 grid(max_tiles * n_kv);
   launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table,
                 table_width, cu_tokens, kv_lens, n_entries, n_heads, n_kv, page_size, n_pages, window, scale_log2e, g_attn_err,
-                cap_c1, cap_c2, sink, keep_first);
+                cap_c1, cap_c2, sink, keep_first, head_values, chunk);
   LLMK_LAUNCH_CHECK("attention_tc");
 }
 
@@ -564,9 +586,13 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
                                const void* v_pages, int n_pages, const int* block_table, int table_width,
                                const int* cu_tokens, const int* kv_lens, int n_tokens, int n_entries, int n_heads,
                                int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream,
-                               float softcap, int sink, int keep_first) {
+                               float softcap, int sink, int keep_first, const float* head_values, int chunk, int sigmoid) {
   if (n_tokens == 0 || n_entries == 0) return 0;
   LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_tc: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
+  LLMK_REQUIRE(chunk >= 0 && (!sigmoid || (head_values && softcap == 0.f)), "attention_tc: bad chunk %d, or sigmoid weights without their biases or with a soft cap", chunk);
+  if (chunk > 0) window = 0;                  // the chunked mask takes the window's place
+  if (sigmoid) sink = 0;
+  if (head_values && !sigmoid) sink = 1;
   if (window == 0) keep_first = 0;
   LLMK_REQUIRE(llmk_attention_tc_supported(n_heads, n_kv, head_dim, page_size),
                "attention_tc: needs head_dim 64 or 128, page_size 16/32/64/128 and at most %d query heads per kv head "
@@ -583,12 +609,13 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
   if ((rc = get_map3(&mv, v_pages, head_dim, page_size, (uint64_t)n_pages * n_kv, head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
   const float scale_log2e = scale * 1.4426950408889634f;
   const float c1 = softcap > 0.f ? scale / softcap : 0.f, c2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
-#define LLMK_ATTN_TC(HS, EXT)                                                                                             \
-  launch<HS, EXT>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles, n_heads, \
-                  n_kv, page_size, n_pages, window, scale_log2e, stream, c1, c2, sink, keep_first)
-  const bool ext = softcap > 0.f || sink || keep_first > 0;
-  if (head_dim == 64) return ext ? LLMK_ATTN_TC(64, true) : LLMK_ATTN_TC(64, false);
-  return ext ? LLMK_ATTN_TC(128, true) : LLMK_ATTN_TC(128, false);
+#define LLMK_ATTN_TC(HS, MODE)                                                                                             \
+  launch<HS, MODE>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles, n_heads, \
+                   n_kv, page_size, n_pages, window, scale_log2e, stream, c1, c2, sink, keep_first, head_values, chunk)
+  const bool ext = softcap > 0.f || sink || keep_first > 0 || chunk > 0;
+  if (sigmoid) return head_dim == 64 ? LLMK_ATTN_TC(64, MODE_SIG) : LLMK_ATTN_TC(128, MODE_SIG);
+  if (head_dim == 64) return ext ? LLMK_ATTN_TC(64, MODE_EXT) : LLMK_ATTN_TC(64, MODE_PLAIN);
+  return ext ? LLMK_ATTN_TC(128, MODE_EXT) : LLMK_ATTN_TC(128, MODE_PLAIN);
 #undef LLMK_ATTN_TC
 }
 

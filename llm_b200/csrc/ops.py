@@ -424,12 +424,24 @@ def token_shift(out: torch.Tensor, h: torch.Tensor, mu: torch.Tensor, state: tor
                                    c_int(ctx.n_tokens), c_int(width), c_int(mixes), c_int(_kind(h.dtype)), _stream()))
 
 
+def _segment_scratch(ctx, seg_len: int, seg_state, seg_decay, state_numel: int, decay_numel: int):
+    if not seg_len:
+        return c_void_p(0), c_void_p(0)
+    segs = ctx.n_tokens // seg_len + ctx.n_entries
+    assert seg_state.dtype == seg_decay.dtype == torch.float32 and seg_state.is_contiguous() and seg_decay.is_contiguous()
+    assert seg_state.numel() >= segs * state_numel and seg_decay.numel() >= segs * decay_numel
+    return _ptr(seg_state), _ptr(seg_decay)
+
+
 def wkv_scan(out: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor,
-             bonus: torch.Tensor, state: torch.Tensor, ctx, shift_src=None, shift_state=None) -> None:
+             bonus: torch.Tensor, state: torch.Tensor, ctx, shift_src=None, shift_state=None, seg_len: int = 0,
+             seg_state=None, seg_decay=None) -> None:
     """o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t; S_t = diag(exp(-exp(z_t + z_bias))) S_(t-1) + k_t v_t^T per head (scan.cu).
     r, k, v [T, heads*dim]: column ranges of one projection; z float32 [T, heads*dim]; bonus float32 [heads, dim];
     state float32 [slots, >= heads*dim*dim]; out float32 [T, heads*dim].  shift_src [T, W] / shift_state [slots, >= W]:
-    the last row of every entry is kept there for the next step's token shift."""
+    the last row of every entry is kept there for the next step's token shift.  seg_len > 0: entries run as segments of that
+    many tokens side by side in two passes; seg_state / seg_decay are float32 scratch for n_tokens // seg_len + n_entries
+    segments of heads*dim*dim and heads*dim numbers."""
     for t in (out, r, k, v, z, state):
         _rows_contig(t, "wkv operand")
     heads, dim = bonus.shape
@@ -447,11 +459,15 @@ def wkv_scan(out: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tenso
                                 _ptr(ctx.state_slots), _ptr(ctx.cu_tokens), c_int(ctx.n_entries), c_int(heads), c_int(dim),
                                 _ptr(shift_src), c_longlong(shift_src.stride(0) if shift_src is not None else 0), _ptr(shift_state),
                                 c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width),
-                                c_int(_kind(r.dtype)), _stream()))
+                                c_int(_kind(r.dtype)), _stream(), c_int(ctx.n_tokens), c_int(seg_len),
+                                *_segment_scratch(ctx, seg_len, seg_state, seg_decay, heads * dim * dim, heads * dim)))
+    if seg_len:
+        count_launches(2)
 
 
 def ssd_scan(out: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor,
-             a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, ctx, heads: int, groups: int, dim: int, vdim: int) -> None:
+             a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, ctx, heads: int, groups: int, dim: int, vdim: int,
+             seg_len: int = 0, seg_state=None, seg_decay=None) -> None:
     """S_t = a_t S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + skip x_t per head, dt_t = softplus(dt + dt_bias),
     a_t = exp(-exp(a_log) dt_t) (scan.cu).  x [T, heads*vdim], b and c [T, groups*dim] (one row stride), dt [T, heads];
     dt_bias, a_log, skip float32 [heads]; state float32 [slots, >= heads*dim*vdim]; out float32 [T, heads*vdim]."""
@@ -466,7 +482,10 @@ def ssd_scan(out: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tenso
                                 c_longlong(b.stride(0)), _ptr(dt), c_longlong(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip),
                                 _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.cu_tokens),
                                 c_int(ctx.n_entries), c_int(heads), c_int(groups), c_int(dim), c_int(vdim), c_int(_kind(x.dtype)),
-                                _stream()))
+                                _stream(), c_int(ctx.n_tokens), c_int(seg_len),
+                                *_segment_scratch(ctx, seg_len, seg_state, seg_decay, heads * dim * vdim, heads * dim)))
+    if seg_len:
+        count_launches(2)
 
 
 def group_rmsnorm_gate(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, rows: int, groups: int,
@@ -915,10 +934,14 @@ def attention_tc_supported(dtype, n_heads: int, n_kv: int, head_dim: int, page_s
 def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  block_table: torch.Tensor, cu_tokens: torch.Tensor, kv_lens: torch.Tensor, n_tokens: int,
                  n_entries: int, n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
-                 softcap: float = 0.0, sink: bool = False, keep_first: int = 0) -> None:
+                 softcap: float = 0.0, sink: bool = False, keep_first: int = 0, sink_values=None, chunk: int = 0,
+                 sigmoid_bias=None) -> None:
     """Flash attention on the tensor cores for entries of any length: rows of entry e are
     cu_tokens[e] .. cu_tokens[e+1], its keys (new tokens included) number kv_lens[e].
-    softcap, sink, keep_first: as in paged_attention_generic."""
+    softcap, sink, keep_first, sink_values, chunk, sigmoid_bias: as in paged_attention_generic."""
+    for t in (sink_values, sigmoid_bias):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+    assert sink_values is None or sigmoid_bias is None
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert q.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
@@ -929,7 +952,8 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
         c_int(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_tokens), _ptr(kv_lens),
         c_int(n_tokens), c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]),
         c_int(window or 0), c_float(scale), _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
-        c_int(keep_first or 0)))
+        c_int(keep_first or 0), _ptr(sigmoid_bias if sigmoid_bias is not None else sink_values), c_int(chunk or 0),
+        c_int(int(sigmoid_bias is not None))))
 
 
 def attention_tc_take_error() -> int:
@@ -945,10 +969,16 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
     where it takes the sizes; the general kernel for float32 and for all other sizes (head sizes
     off the 16-grid among them).  value_dim, softcap, sink, keep_first: see paged_attention_generic, the kernel
-    that takes them in every combination.  sink_values (a learned score per head for the sink): the general kernel and the
-    split-key decode kernel; chunk and sigmoid_bias (a chunked mask, sigmoid weights): the general kernel, whose one warp
-    per (token, head) walks at most one chunk of keys."""
+    that takes them in every combination.  sink_values (a learned score per head for the sink), chunk and sigmoid_bias (a
+    chunked mask, sigmoid weights): the tcgen05 kernel for steps with prompt portions where it takes the sizes; else the
+    split-key decode kernel (sink_values) or the general kernel, whose one warp per (token, head) walks at most one chunk."""
     if chunk or sigmoid_bias is not None:
+        if (not ctx.decode_only and not softcap and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
+                and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):
+            attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
+                         ctx.n_entries, n_heads, n_kv, head_dim, 0 if chunk else window, scale, chunk=chunk,
+                         sigmoid_bias=sigmoid_bias)
+            return
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                                 ctx.n_tokens, n_heads, n_kv, head_dim, 0 if chunk else window, scale, value_dim=value_dim,
                                 softcap=softcap, chunk=chunk, sigmoid_bias=sigmoid_bias)
@@ -969,10 +999,11 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
                                n_heads, n_kv, head_dim, window, scale, splits=splits, max_keys=max_keys,
                                softcap=softcap, sink=sink, keep_first=keep_first, sink_values=sink_values)
         return
-    if (extended and sink_values is None and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
+    if (extended and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
             and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):
         attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens,
-                     ctx.n_entries, n_heads, n_kv, head_dim, window, scale, softcap=softcap, sink=sink, keep_first=keep_first)
+                     ctx.n_entries, n_heads, n_kv, head_dim, window, scale, softcap=softcap, sink=sink, keep_first=keep_first,
+                     sink_values=sink_values)
         return
     if extended:
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,

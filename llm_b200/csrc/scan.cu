@@ -14,6 +14,12 @@
 // rows 8 g .., columns 4 j .. in registers; tokens are staged in shared memory CHUNK at a time; the partial outputs of the
 // row groups are summed in the order of g.
 //
+// Long entries (prompts) run as segments of seg_len tokens side by side, as in recurrent.cu: pass 1 walks every segment but
+// an entry's last from a zero state and leaves its end state and the product of its decays; a chain kernel turns those into
+// every segment's true start state (start_(s+1) = diag(P_s) start_s + E_s, from the request's state); pass 2 walks every
+// segment from its true start, writes the outputs, and the entry's last segment writes the request's state.  The float32
+// sums of a token's state are then grouped by where its segment begins, which moves results by rounding only.
+//
 // Also here: the token shift that feeds the bonus form's projections, the gated RMS norm over groups of channels that
 // follows either form, and the mean of two normed rows (two mixers side by side).
 #include "common.cuh"
@@ -38,6 +44,9 @@ struct ScanArgs {
   int heads, qk_heads, dim, vdim;
   // bonus form: the last input row of every entry is kept for the next step's token shift
   const void* shift_src; long long shift_stride; float* shift_state; long long shift_slot_stride; int shift_width;
+  // segments: seg_len 0 = one pass over the whole entry (mode 0); else mode 1 or 2 (the two passes), at most max_segs
+  // segments per entry, seg_state [segments, heads, dim, vdim] and seg_decay [segments, heads, dim] float32 scratch
+  int seg_len, max_segs, mode; float* seg_state; float* seg_decay;
 };
 
 template <typename T, int VT, int FORM>
@@ -55,15 +64,30 @@ diag_scan_kernel(ScanArgs a) {
   float* part = v_s + CHUNK * VT;             // [CHUNK][groups][VT]
   const int j = threadIdx.x, g = threadIdx.y;
   const int tid = g * TX + j, nthreads = TX * groups;
-  const int entry = blockIdx.z, head = blockIdx.y;
+  const int mode = a.mode;
+  const int entry = a.seg_len ? blockIdx.z / a.max_segs : blockIdx.z, head = blockIdx.y;
   const int qk_head = head / (a.heads / a.qk_heads);
   const int col0 = blockIdx.x * VT + j * COLS;
   const int dim = a.dim, vdim = a.vdim;
-  const int t0 = a.cu_tokens[entry], t1 = a.cu_tokens[entry + 1];
+  int t0 = a.cu_tokens[entry], t1 = a.cu_tokens[entry + 1];
+  const int t_end = t1;
+  size_t seg_index = 0;
+  if (a.seg_len) {
+    const int seg = blockIdx.z % a.max_segs;
+    if (seg * a.seg_len >= t1 - t0) return;
+    for (int e = 0; e < entry; ++e) seg_index += (a.cu_tokens[e + 1] - a.cu_tokens[e] + a.seg_len - 1) / a.seg_len;
+    seg_index += seg;
+    t0 += seg * a.seg_len;
+    t1 = min(t1, t0 + a.seg_len);
+    if (mode == 1 && t1 == t_end) return;               // nothing follows an entry's last segment
+  }
+  const bool last = t1 == t_end;
   const T *q = (const T*)a.q, *k = (const T*)a.k, *v = (const T*)a.v;
-  float* S_g = a.state + (size_t)a.state_slots[entry] * a.slot_stride + ((size_t)head * dim) * vdim;
+  float* S_slot = a.state + (size_t)a.state_slots[entry] * a.slot_stride + ((size_t)head * dim) * vdim;
+  float* S_seg = a.seg_state + ((seg_index * a.heads + head) * dim) * vdim;
+  float* S_g = mode == 0 ? S_slot : S_seg;
 
-  if (FORM == FORM_BONUS && a.shift_state && blockIdx.x == 0 && head == 0 && t1 > t0) {
+  if (FORM == FORM_BONUS && a.shift_state && blockIdx.x == 0 && head == 0 && t1 > t0 && last && mode != 1) {
     const T* src = (const T*)a.shift_src + (size_t)(t1 - 1) * a.shift_stride;
     float* dst = a.shift_state + (size_t)a.state_slots[entry] * a.shift_slot_stride;
     for (int c = tid; c < a.shift_width; c += nthreads) dst[c] = to_f32(src[c]);
@@ -74,9 +98,12 @@ diag_scan_kernel(ScanArgs a) {
   for (int r = 0; r < ROWS; ++r) {
     const int d = g * ROWS + r;
 #pragma unroll
-    for (int c = 0; c < COLS; ++c) S[r][c] = (d < dim && col0 + c < vdim) ? S_g[(size_t)d * vdim + col0 + c] : 0.f;
+    for (int c = 0; c < COLS; ++c) S[r][c] = (mode != 1 && d < dim && col0 + c < vdim) ? S_g[(size_t)d * vdim + col0 + c] : 0.f;
     U[r] = (FORM == FORM_BONUS && d < dim) ? a.bonus[head * dim + d] : 0.f;
   }
+  float A[ROWS];                              // pass 1: the product of the segment's decays, per key channel
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) A[r] = 1.f;
   const float neg_a = FORM == FORM_SCALAR ? -expf(a.a_log[head]) : 0.f;
   const float skip = FORM == FORM_SCALAR ? a.skip[head] : 0.f;
   const float dt_b = FORM == FORM_SCALAR ? a.dt_bias[head] : 0.f;
@@ -127,6 +154,10 @@ diag_scan_kernel(ScanArgs a) {
           ac[r] = ac[r + 1] = ac[r + 2] = ac[r + 3] = a_tok;
         }
       }
+      if (mode == 1) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) A[r] *= ac[r];
+      }
       float o[COLS] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
@@ -142,9 +173,10 @@ diag_scan_kernel(ScanArgs a) {
           }
         }
       }
-      *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
+      if (mode != 1) *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
     }
     __syncthreads();
+    if (mode == 1) continue;                  // pass 1 writes no outputs
     for (int idx = tid; idx < n * VT; idx += nthreads) {
       const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
       if (cc >= vdim) continue;
@@ -154,26 +186,80 @@ diag_scan_kernel(ScanArgs a) {
       a.out[(size_t)(c0 + c) * a.out_stride + (size_t)head * vdim + cc] = o;
     }
   }
+  if (mode == 2 && !last) return;             // pass 2: only an entry's last segment ends at the request's new state
+  float* S_out = mode == 1 ? S_seg : S_slot;
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
     const int d = g * ROWS + r;
     if (d >= dim) continue;
 #pragma unroll
     for (int c = 0; c < COLS; ++c)
-      if (col0 + c < vdim) S_g[(size_t)d * vdim + col0 + c] = S[r][c];
+      if (col0 + c < vdim) S_out[(size_t)d * vdim + col0 + c] = S[r][c];
+    if (mode == 1 && blockIdx.x == 0 && j == 0) a.seg_decay[(seg_index * a.heads + head) * dim + d] = A[r];
   }
 }
 
+// Chains the segments of every entry: seg_state[s] holds the segment's end state from zero on entry (but for an entry's
+// last segment, which holds nothing) and its true start state on exit.  A thread per element of the state.
+__global__ void __launch_bounds__(256)
+scan_chain_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay, const float* __restrict__ state,
+                  long long slot_stride, const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, int heads,
+                  int dim, int vdim, int seg_len) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t per = (size_t)heads * dim * vdim;
+  const size_t el = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (el >= per) return;
+  const int entry = blockIdx.y;
+  const size_t row = el / vdim;               // head * dim + d
+  size_t seg0 = 0;
+  for (int e = 0; e < entry; ++e) seg0 += (cu_tokens[e + 1] - cu_tokens[e] + seg_len - 1) / seg_len;
+  const int n_seg = (cu_tokens[entry + 1] - cu_tokens[entry] + seg_len - 1) / seg_len;
+  float S = state[(size_t)state_slots[entry] * slot_stride + el];
+  for (int s = 0; s < n_seg; ++s) {
+    float* at = seg_state + (seg0 + s) * per + el;
+    const float local = s + 1 < n_seg ? *at : 0.f;
+    *at = S;
+    if (s + 1 < n_seg) S = fmaf(seg_decay[(seg0 + s) * heads * dim + row], S, local);
+  }
+}
+
+#define SCAN_CHECK(name)                                                   \
+  do {                                                                     \
+    cudaError_t e__ = cudaPeekAtLastError();                               \
+    if (e__ != cudaSuccess) {                                              \
+      cudaGetLastError();                                                  \
+      return llmk_fail((int)e__, "%s: %s", name, cudaGetErrorString(e__)); \
+    }                                                                      \
+  } while (0)
+
+// seg_len > 0: two passes over segments with the chain between them; n_tokens is then the step's number of tokens and
+// seg_state / seg_decay hold n_tokens / seg_len + n_entries segments.
 template <typename T, int FORM>
-int launch_scan(const ScanArgs& a, int n_entries, cudaStream_t stream) {
+int launch_scan(ScanArgs a, int n_entries, int n_tokens, int seg_len, float* seg_state, float* seg_decay, cudaStream_t stream) {
   constexpr int VT = 32;
+  LLMK_REQUIRE(seg_len >= 0 && (seg_len == 0 || (seg_state && seg_decay && n_tokens > 0)), "scan: segments need their scratch");
   const int groups = (a.dim + ROWS - 1) / ROWS;
   const size_t smem = ((size_t)3 * CHUNK * groups * ROWS + CHUNK * VT + (size_t)CHUNK * groups * VT) * sizeof(float);
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(diag_scan_kernel<T, VT, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_kernel(diag_scan_kernel<T, VT, FORM>, dim3((a.vdim + VT - 1) / VT, a.heads, n_entries), dim3(VT / COLS, groups), smem,
-                stream, a);
-  LLMK_LAUNCH_CHECK("diag_scan");
+  const int max_segs = seg_len ? (n_tokens - (n_entries - 1) + seg_len - 1) / seg_len : 1;
+  LLMK_REQUIRE((long long)n_entries * max_segs <= 65535, "scan: too many segments for one launch");
+  a.seg_len = seg_len; a.max_segs = max_segs; a.seg_state = seg_state; a.seg_decay = seg_decay;
+  const dim3 grid((a.vdim + VT - 1) / VT, a.heads, n_entries * max_segs), block(VT / COLS, groups);
+  for (int mode = seg_len ? 1 : 0; mode <= (seg_len ? 2 : 0); ++mode) {
+    a.mode = mode;
+    launch_kernel(diag_scan_kernel<T, VT, FORM>, grid, block, smem, stream, a);
+    SCAN_CHECK("diag_scan");
+    if (mode == 1) {
+      const size_t per = (size_t)a.heads * a.dim * a.vdim;
+      launch_kernel(scan_chain_kernel, dim3((unsigned)((per + 255) / 256), n_entries), dim3(256), 0, stream, seg_state,
+                    (const float*)seg_decay, (const float*)a.state, a.slot_stride, a.state_slots, a.cu_tokens, a.heads, a.dim,
+                    a.vdim, seg_len);
+      SCAN_CHECK("scan_chain");
+    }
+  }
+  return 0;
 }
 
 // ---- token shift -------------------------------------------------------------------------------------------
@@ -273,7 +359,8 @@ LLMK_API int llmk_wkv_scan(float* out, long long out_stride, const void* r, cons
                            const float* z, long long z_stride, const float* z_bias, const float* bonus, float* state,
                            long long slot_stride, const int* state_slots, const int* cu_tokens, int n_entries, int heads, int dim,
                            const void* shift_src, long long shift_stride, float* shift_state, long long shift_slot_stride,
-                           int shift_width, int dtype, cudaStream_t stream) {
+                           int shift_width, int dtype, cudaStream_t stream, int n_tokens, int seg_len, float* seg_state,
+                           float* seg_decay) {
   if (n_entries == 0) return 0;
   LLMK_REQUIRE(dim > 0 && dim <= ROWS * MAX_GROUPS, "wkv_scan: head size %d (1 to %d)", dim, ROWS * MAX_GROUPS);
   ScanArgs a = {};
@@ -282,14 +369,17 @@ LLMK_API int llmk_wkv_scan(float* out, long long out_stride, const void* r, cons
   a.state_slots = state_slots; a.cu_tokens = cu_tokens; a.heads = a.qk_heads = heads; a.dim = a.vdim = dim;
   a.shift_src = shift_src; a.shift_stride = shift_stride; a.shift_state = shift_state; a.shift_slot_stride = shift_slot_stride;
   a.shift_width = shift_width;
-  return dispatch_dtype(dtype, [&](auto* tag) { return launch_scan<LLMK_ELEM(tag), FORM_BONUS>(a, n_entries, stream); });
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    return launch_scan<LLMK_ELEM(tag), FORM_BONUS>(a, n_entries, n_tokens, seg_len, seg_state, seg_decay, stream);
+  });
 }
 
 // The scalar form.  x [T, heads * vdim], b and c [T, groups * dim] (one row stride bc_stride), dt [T, heads].
 LLMK_API int llmk_ssd_scan(float* out, long long out_stride, const void* x, long long x_stride, const void* b, const void* c,
                            long long bc_stride, const void* dt, long long dt_stride, const float* dt_bias, const float* a_log,
                            const float* skip, float* state, long long slot_stride, const int* state_slots, const int* cu_tokens,
-                           int n_entries, int heads, int groups, int dim, int vdim, int dtype, cudaStream_t stream) {
+                           int n_entries, int heads, int groups, int dim, int vdim, int dtype, cudaStream_t stream, int n_tokens,
+                           int seg_len, float* seg_state, float* seg_decay) {
   if (n_entries == 0) return 0;
   LLMK_REQUIRE(dim > 0 && dim <= ROWS * MAX_GROUPS, "ssd_scan: state size %d (1 to %d)", dim, ROWS * MAX_GROUPS);
   LLMK_REQUIRE(groups > 0 && heads % groups == 0, "ssd_scan: %d heads do not divide into %d groups", heads, groups);
@@ -298,7 +388,9 @@ LLMK_API int llmk_ssd_scan(float* out, long long out_stride, const void* x, long
   a.dt = dt; a.dt_stride = dt_stride; a.dt_bias = dt_bias; a.a_log = a_log; a.skip = skip; a.state = state;
   a.slot_stride = slot_stride; a.state_slots = state_slots; a.cu_tokens = cu_tokens; a.heads = heads; a.qk_heads = groups;
   a.dim = dim; a.vdim = vdim;
-  return dispatch_dtype(dtype, [&](auto* tag) { return launch_scan<LLMK_ELEM(tag), FORM_SCALAR>(a, n_entries, stream); });
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    return launch_scan<LLMK_ELEM(tag), FORM_SCALAR>(a, n_entries, n_tokens, seg_len, seg_state, seg_decay, stream);
+  });
 }
 
 LLMK_API int llmk_group_rmsnorm_gate(void* out, const float* x, const float* w, const void* gate, long long gate_stride,

@@ -39,6 +39,20 @@ def _state_numel(need) -> int:
     return n
 
 
+SEGMENT = 64       # tokens per segment of a prompt step (csrc/scan.cu)
+
+
+def _segments(ctx, tag: str, state_numel: int, decay_numel: int):
+    """(seg_len, seg_state, seg_decay): a step with prompt portions runs them as segments side by side in two passes;
+    single tokens and short steps take one pass."""
+    if ctx.decode_only or ctx.n_tokens < 4 * SEGMENT:
+        return 0, None, None
+    ws = ctx.workspace
+    cap = ws.max_rows // SEGMENT + ctx.cu_tokens.numel()
+    return (SEGMENT, ws.flat(tag + "_seg_state", cap * state_numel, torch.float32),
+            ws.flat(tag + "_seg_decay", cap * decay_numel, torch.float32))
+
+
 def _sub_view(view, state):
     """The layer's view as an inner part sees it: the same cache, its own columns of the state row."""
     return dataclasses.replace(view, state=state)
@@ -106,8 +120,9 @@ class TimeMixWKV(Part):
         # the decay's pre-activation in float32; bias and the two exponentials are the recurrence kernel's
         z = linear(low_t, self.w2, ws.get("wkv_z", T, I, torch.float32), T)
         o = ws.get("wkv_o", T, I, torch.float32)
+        seg, seg_state, seg_decay = _segments(ctx, "wkv", I * self.head_dim, I)
         ops.wkv_scan(o, rkvg[:, :I], rkvg[:, I:2 * I], rkvg[:, 2 * I:3 * I], z, self.w0, self.bonus, S, ctx,
-                     shift_src=x, shift_state=shift)
+                     shift_src=x, shift_state=shift, seg_len=seg, seg_state=seg_state, seg_decay=seg_decay)
         normed = ws.get("attn_out", T, I, self.dtype)
         ops.group_rmsnorm_gate(normed, o, self.gain, rkvg[:, 3 * I:], T, self.num_heads, self.eps)
         return linear(normed, self.w_o, ws.get("mixer_out", T, W, self.dtype), T, allow_partial=FUSE_PARTIALS)
@@ -166,8 +181,9 @@ class StateSpaceDuality(Part):
         xbc = ws.get("ssd_xbc", T, C, self.dtype)
         ops.short_conv(xbc, proj[:, I:I + C], self.w_conv, self.b_conv, conv_state, ctx, silu=True)
         y = ws.get("ssd_y", T, I, torch.float32)
+        seg, seg_state, seg_decay = _segments(ctx, "ssd", H * self.state_size * self.value_dim, H * self.state_size)
         ops.ssd_scan(y, xbc[:, :I], xbc[:, I:I + GN], xbc[:, I + GN:], proj[:, I + C:], self.dt_bias, self.a_log, self.skip,
-                     S, ctx, H, self.groups, self.state_size, self.value_dim)
+                     S, ctx, H, self.groups, self.state_size, self.value_dim, seg_len=seg, seg_state=seg_state, seg_decay=seg_decay)
         normed = ws.get("ssd_normed", T, I, self.dtype)
         ops.group_rmsnorm_gate(normed, y, self.gain, proj[:, :I], T, self.norm_groups, self.eps, gate_first=True)
         return linear(normed, self.w_o, ws.get("ssd_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)

@@ -156,10 +156,38 @@ def make_weights(cfg: dict, seed: int, peak: float = 1.5, decay_rank: int = 6, s
     return w
 
 
-def random_config(seed: int) -> dict:
+def random_layerlike_config(rng) -> dict:
+    """Sizes of some hundreds, heads of 32 to 128: what the tensor-core kernels take, with the odd size between."""
+    width = rng.choice([192, 256, 320, 384, 512])
+    layers = []
+    for n in range(rng.randint(3, 6)):
+        pick = (n + rng.randint(0, 2)) % 3
+        if pick == 0:
+            mixer = wkv(rng.randint(2, 8), rng.choice([32, 48, 64, 96]))
+        elif pick == 1:
+            rot = rng.choice([16, 32, 64])
+            mixer = latent(rng.choice([2, 4, 6, 8, 12]), rng.choice([32, 64, 96, 128]), rot, rng.choice([32, 64, 128]),
+                           rng.choice([64, 96, 128, 192]), rng.choice([48, 80, 128]), size=rng.choice([48, 100, 129, 256, 1000]),
+                           scale=rng.uniform(0.05, 0.2), base=rng.choice([10000.0, 50000.0, 1e6]))
+        else:
+            kv, dim, groups = rng.choice([1, 2, 4]), rng.choice([32, 64, 128]), rng.choice([1, 2, 4])
+            s_heads, s_vdim = groups * rng.choice([1, 2, 4]), rng.choice([32, 48, 64])
+            ng = rng.choice([d for d in (1, 2, 4, 8) if (s_heads * s_vdim) % d == 0])
+            mixer = parallel(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([32, 64, 128]), chunk=rng.choice([32, 64, 96, 100, 128, 512]),
+                             rot_dims=rng.choice([dim, dim, dim // 2, 0]), scale=rng.uniform(0.05, 0.2), s_heads=s_heads, s_vdim=s_vdim,
+                             state=rng.choice([32, 48, 64, 128]), groups=groups, norm_groups=ng, conv=rng.randint(2, 4),
+                             base=rng.choice([10000.0, 1e6]))
+        mlp = dense(rng.choice([256, 344, 512]), rng.choice([1.0, 2.5, 7.0])) if rng.random() < 0.7 else None
+        layers.append(layer(mixer, mlp))
+    return config(width, rng.choice([384, 500, 1000]), rng.randint(2, 4), rng.randint(2, 4), layers, eps=rng.choice([1e-6, 1e-5]))
+
+
+def random_config(seed: int, large: bool = False) -> dict:
     """Sizes, constants and layer order drawn from a seed."""
     import random
     rng = random.Random(seed)
+    if large:
+        return random_layerlike_config(rng)
     width = rng.choice([40, 56, 72, 88, 100, 128, 136])
     layers = []
     for _ in range(rng.randint(2, 5)):
