@@ -92,6 +92,77 @@ hc_norm_kernel(float* __restrict__ resid, MaybePartial<T> y, const float* __rest
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[(size_t)t * hidden + c] = from_f32<T>(u_s[c] * r);
 }
 
+// The same with the stream count known at compile time and eight columns per thread: every access is 16 bytes wide
+// (width a multiple of 8), the streams of a column group stay in registers between the write and the read.
+template <typename T, int S>
+__global__ void __launch_bounds__(256)
+hc_norm_vec_kernel(float* __restrict__ resid, MaybePartial<T> y, const float* __restrict__ write_mix,
+                   const float* __restrict__ write_out, const float* __restrict__ read_in, const float* __restrict__ gain,
+                   T* __restrict__ out, int hidden, float eps) {
+  extern __shared__ float u_s[];               // [hidden]
+  __shared__ float red[32];
+  __shared__ float mix_s[S * S], wout_s[S], win_s[S];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const bool pending = write_mix != nullptr;
+  if (threadIdx.x < S * S && pending) mix_s[threadIdx.x] = write_mix[threadIdx.x];
+  if (threadIdx.x < S) {
+    wout_s[threadIdx.x] = pending ? write_out[threadIdx.x] : 0.f;
+    win_s[threadIdx.x] = out ? read_in[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  float* row = resid + (size_t)t * hidden * S;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float x[S][8];
+#pragma unroll
+    for (int s = 0; s < S; ++s) Vec8<float>::load(row + (size_t)s * hidden + c, x[s]);
+    if (pending) {
+      float yv[8];
+      y.at8((size_t)t * hidden + c, yv);
+      float xn[S][8];
+#pragma unroll
+      for (int to = 0; to < S; ++to) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float a = 0.f;
+#pragma unroll
+          for (int s = 0; s < S; ++s) a = fmaf(mix_s[s * S + to], x[s][i], a);
+          xn[to][i] = fmaf(wout_s[to], yv[i], a);
+        }
+        Vec8<float>::store(row + (size_t)to * hidden + c, xn[to]);
+      }
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[s][i] = xn[s][i];
+    }
+    if (out) {
+      float u[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float a = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) a = fmaf(win_s[s], x[s][i], a);
+        u[i] = a;
+        ss = fmaf(a, a, ss);
+      }
+      Vec8<float>::store(u_s + c, u);
+    }
+  }
+  if (!out) return;
+  const float total = block_sum(ss, red);
+  const float r = 1.f / sqrtf(total / (float)hidden + eps) * gain[0];
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float u[8];
+    Vec8<float>::load(u_s + c, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u[i] *= r;
+    Vec8<T>::store(out + (size_t)t * hidden + c, u);
+  }
+}
+
 __global__ void hc_gather_sum_kernel(float* __restrict__ out, const float* __restrict__ resid, const int* __restrict__ rows,
                                      int hidden, int streams) {
   pdl_launch_dependents();
@@ -148,6 +219,21 @@ LLMK_API int llmk_hc_norm(float* resid, const void* y, const float* partials, in
     using T = LLMK_ELEM(tag);
     MaybePartial<T> yy{(const T*)y, partials, splits, split_stride};
     const size_t smem = (size_t)hidden * sizeof(float);
+    const bool vec = hidden % 8 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)partials % 16 == 0 &&
+                     split_stride % 4 == 0 && (uintptr_t)out % 16 == 0;
+#define LLMK_HC_VEC(S)                                                                                                  \
+  case S:                                                                                                               \
+    if (smem > 48 * 1024)                                                                                               \
+      cudaFuncSetAttribute(hc_norm_vec_kernel<T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+    launch_kernel(hc_norm_vec_kernel<T, S>, dim3(n_tokens), dim3(256), smem, stream, resid, yy, write_mix, write_out,   \
+                  read_in, gain, (T*)out, hidden, eps);                                                                 \
+    LLMK_LAUNCH_CHECK("hc_norm");
+    if (vec) {
+      switch (streams) {
+        LLMK_HC_VEC(1) LLMK_HC_VEC(2) LLMK_HC_VEC(3) LLMK_HC_VEC(4) LLMK_HC_VEC(5) LLMK_HC_VEC(6) LLMK_HC_VEC(7) LLMK_HC_VEC(8)
+      }
+    }
+#undef LLMK_HC_VEC
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(hc_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_kernel(hc_norm_kernel<T>, dim3(n_tokens), dim3(256), smem, stream, resid, yy, write_mix, write_out, read_in, gain,

@@ -49,13 +49,15 @@ struct ScanArgs {
   int seg_len, max_segs, mode; float* seg_state; float* seg_decay;
 };
 
-template <typename T, int VT, int FORM>
-__global__ void __launch_bounds__(VT / COLS * MAX_GROUPS)
+// STATE_ONLY: the first pass over segments, which needs end states and decay products but no outputs (no q, no sums).
+template <typename T, int VT, int FORM, bool STATE_ONLY>
+__global__ void __launch_bounds__(VT / COLS * MAX_GROUPS, 2)
 diag_scan_kernel(ScanArgs a) {
   extern __shared__ __align__(16) float smem[];
   pdl_launch_dependents();
   pdl_wait();
   constexpr int TX = VT / COLS;
+  static_assert(TX == ROWS, "a thread stages the channel of its own index: threads per row group = rows per group");
   const int groups = blockDim.y, dpad = groups * ROWS;
   float* q_s = smem;                          // [CHUNK][dpad]
   float* k_s = q_s + CHUNK * dpad;
@@ -108,34 +110,72 @@ diag_scan_kernel(ScanArgs a) {
   const float skip = FORM == FORM_SCALAR ? a.skip[head] : 0.f;
   const float dt_b = FORM == FORM_SCALAR ? a.dt_bias[head] : 0.f;
 
+  // What a thread brings of a chunk: channel d = tid of every token's q, k (and z), and up to VREGS of its values.  The
+  // next chunk's loads are issued before this chunk's multiply-adds and land under them.
+  constexpr int VREGS = 8;
+  const bool v_regs = CHUNK * VT <= VREGS * nthreads;       // else (fewer than 32 channels) the values are read when staged
+  T q_r[CHUNK], k_r[CHUNK], v_r[VREGS], dt_r;
+  float z_r[CHUNK];
+  const float zb = (FORM == FORM_BONUS && tid < dim) ? a.z_bias[head * dim + tid] : 0.f;
+  auto fetch = [&](int c0) {
+    const int n = min(CHUNK, t1 - c0);
+#pragma unroll
+    for (int c = 0; c < CHUNK; ++c) {
+      if (c < n && tid < dim) {
+        const size_t at = (size_t)(c0 + c) * a.qk_stride + (size_t)qk_head * dim + tid;
+        if (!STATE_ONLY) q_r[c] = q[at];
+        k_r[c] = k[at];
+        if (FORM == FORM_BONUS) z_r[c] = a.z[(size_t)(c0 + c) * a.z_stride + (size_t)head * dim + tid];
+      }
+    }
+    if (v_regs) {
+#pragma unroll
+      for (int i = 0; i < VREGS; ++i) {
+        const int idx = tid + i * nthreads, cc = blockIdx.x * VT + idx % VT;
+        if (idx < n * VT && cc < vdim) v_r[i] = v[(size_t)(c0 + idx / VT) * a.v_stride + (size_t)head * vdim + cc];
+      }
+    }
+    if (FORM == FORM_SCALAR && tid < n) dt_r = ((const T*)a.dt)[(size_t)(c0 + tid) * a.dt_stride + head];
+  };
+  if (t0 < t1) fetch(t0);
+
   for (int c0 = t0; c0 < t1; c0 += CHUNK) {
     const int n = min(CHUNK, t1 - c0);
     __syncthreads();                          // the previous chunk's partial sums have been read
     if (FORM == FORM_SCALAR) {
-      if (tid < n) a_s[tid] = softplus_f(to_f32(((const T*)a.dt)[(size_t)(c0 + tid) * a.dt_stride + head]) + dt_b);
+      if (tid < n) a_s[tid] = softplus_f(to_f32(dt_r) + dt_b);
       __syncthreads();
     }
-    for (int c = 0; c < n; ++c) {
-      for (int d = tid; d < dpad; d += nthreads) {
-        float qv = 0.f, kv = 0.f, av = 0.f;
-        if (d < dim) {
-          const size_t at = (size_t)(c0 + c) * a.qk_stride + (size_t)qk_head * dim + d;
-          qv = to_f32(q[at]);
-          kv = to_f32(k[at]);
-          if (FORM == FORM_BONUS)
-            av = expf(-expf(a.z[(size_t)(c0 + c) * a.z_stride + (size_t)head * dim + d] + a.z_bias[head * dim + d]));
-          else
-            kv *= a_s[c];                     // dt B
-        }
-        q_s[c * dpad + d] = qv; k_s[c * dpad + d] = kv;
-        if (FORM == FORM_BONUS) a_s[c * dpad + d] = av;
+#pragma unroll
+    for (int c = 0; c < CHUNK; ++c) {
+      if (c >= n) break;
+      float qv = 0.f, kv = 0.f, av = 0.f;
+      if (tid < dim) {
+        if (!STATE_ONLY) qv = to_f32(q_r[c]);
+        kv = to_f32(k_r[c]);
+        if (FORM == FORM_BONUS)
+          av = expf(-expf(z_r[c] + zb));
+        else
+          kv *= a_s[c];                       // dt B
+      }
+      if (!STATE_ONLY) q_s[c * dpad + tid] = qv;
+      k_s[c * dpad + tid] = kv;
+      if (FORM == FORM_BONUS) a_s[c * dpad + tid] = av;
+    }
+    if (v_regs) {
+#pragma unroll
+      for (int i = 0; i < VREGS; ++i) {
+        const int idx = tid + i * nthreads;
+        if (idx < n * VT) v_s[idx] = blockIdx.x * VT + idx % VT < vdim ? to_f32(v_r[i]) : 0.f;
+      }
+    } else {
+      for (int idx = tid; idx < n * VT; idx += nthreads) {
+        const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
+        v_s[idx] = cc < vdim ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)head * vdim + cc]) : 0.f;
       }
     }
-    for (int idx = tid; idx < n * VT; idx += nthreads) {
-      const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
-      v_s[idx] = cc < vdim ? to_f32(v[(size_t)(c0 + c) * a.v_stride + (size_t)head * vdim + cc]) : 0.f;
-    }
     __syncthreads();
+    if (c0 + CHUNK < t1) fetch(c0 + CHUNK);
     for (int c = 0; c < n; ++c) {
       const float4 v4 = *reinterpret_cast<const float4*>(v_s + c * VT + j * COLS);
       const float vv[COLS] = {v4.x, v4.y, v4.z, v4.w};
@@ -144,9 +184,11 @@ diag_scan_kernel(ScanArgs a) {
 #pragma unroll
       for (int r = 0; r < ROWS; r += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(k_s + c * dpad + g * ROWS + r);
-        const float4 q4 = *reinterpret_cast<const float4*>(q_s + c * dpad + g * ROWS + r);
         kc[r] = k4.x; kc[r + 1] = k4.y; kc[r + 2] = k4.z; kc[r + 3] = k4.w;
-        qc[r] = q4.x; qc[r + 1] = q4.y; qc[r + 2] = q4.z; qc[r + 3] = q4.w;
+        if (!STATE_ONLY) {
+          const float4 q4 = *reinterpret_cast<const float4*>(q_s + c * dpad + g * ROWS + r);
+          qc[r] = q4.x; qc[r + 1] = q4.y; qc[r + 2] = q4.z; qc[r + 3] = q4.w;
+        }
         if (FORM == FORM_BONUS) {
           const float4 a4 = *reinterpret_cast<const float4*>(a_s + c * dpad + g * ROWS + r);
           ac[r] = a4.x; ac[r + 1] = a4.y; ac[r + 2] = a4.z; ac[r + 3] = a4.w;
@@ -154,7 +196,7 @@ diag_scan_kernel(ScanArgs a) {
           ac[r] = ac[r + 1] = ac[r + 2] = ac[r + 3] = a_tok;
         }
       }
-      if (mode == 1) {
+      if (STATE_ONLY) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) A[r] *= ac[r];
       }
@@ -164,7 +206,9 @@ diag_scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int cc = 0; cc < COLS; ++cc) {
           const float kv = kc[r] * vv[cc];
-          if (FORM == FORM_BONUS) {
+          if (STATE_ONLY) {
+            S[r][cc] = fmaf(ac[r], S[r][cc], kv);
+          } else if (FORM == FORM_BONUS) {
             o[cc] = fmaf(fmaf(U[r], kv, S[r][cc]), qc[r], o[cc]);      // the old state plus the bonus for the current token
             S[r][cc] = fmaf(ac[r], S[r][cc], kv);
           } else {
@@ -173,10 +217,10 @@ diag_scan_kernel(ScanArgs a) {
           }
         }
       }
-      if (mode != 1) *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
+      if (!STATE_ONLY) *reinterpret_cast<float4*>(part + (c * groups + g) * VT + j * COLS) = make_float4(o[0], o[1], o[2], o[3]);
     }
+    if (STATE_ONLY) continue;                 // the first pass writes no outputs
     __syncthreads();
-    if (mode == 1) continue;                  // pass 1 writes no outputs
     for (int idx = tid; idx < n * VT; idx += nthreads) {
       const int c = idx / VT, jj = idx % VT, cc = blockIdx.x * VT + jj;
       if (cc >= vdim) continue;
@@ -216,11 +260,21 @@ scan_chain_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_d
   for (int e = 0; e < entry; ++e) seg0 += (cu_tokens[e + 1] - cu_tokens[e] + seg_len - 1) / seg_len;
   const int n_seg = (cu_tokens[entry + 1] - cu_tokens[entry] + seg_len - 1) / seg_len;
   float S = state[(size_t)state_slots[entry] * slot_stride + el];
-  for (int s = 0; s < n_seg; ++s) {
-    float* at = seg_state + (seg0 + s) * per + el;
-    const float local = s + 1 < n_seg ? *at : 0.f;
-    *at = S;
-    if (s + 1 < n_seg) S = fmaf(seg_decay[(seg0 + s) * heads * dim + row], S, local);
+  // eight segments' loads are issued together; the chain itself is one multiply-add a segment
+  for (int s0 = 0; s0 < n_seg; s0 += 8) {
+    float local[8], decay[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool inner = s0 + i + 1 < n_seg;
+      local[i] = inner ? seg_state[(seg0 + s0 + i) * per + el] : 0.f;
+      decay[i] = inner ? seg_decay[(seg0 + s0 + i) * heads * dim + row] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (s0 + i >= n_seg) break;
+      seg_state[(seg0 + s0 + i) * per + el] = S;
+      S = fmaf(decay[i], S, local[i]);
+    }
   }
 }
 
@@ -242,14 +296,20 @@ int launch_scan(ScanArgs a, int n_entries, int n_tokens, int seg_len, float* seg
   const int groups = (a.dim + ROWS - 1) / ROWS;
   const size_t smem = ((size_t)3 * CHUNK * groups * ROWS + CHUNK * VT + (size_t)CHUNK * groups * VT) * sizeof(float);
   if (smem > 48 * 1024)
-    cudaFuncSetAttribute(diag_scan_kernel<T, VT, FORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  {
+    cudaFuncSetAttribute(diag_scan_kernel<T, VT, FORM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(diag_scan_kernel<T, VT, FORM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   const int max_segs = seg_len ? (n_tokens - (n_entries - 1) + seg_len - 1) / seg_len : 1;
   LLMK_REQUIRE((long long)n_entries * max_segs <= 65535, "scan: too many segments for one launch");
   a.seg_len = seg_len; a.max_segs = max_segs; a.seg_state = seg_state; a.seg_decay = seg_decay;
   const dim3 grid((a.vdim + VT - 1) / VT, a.heads, n_entries * max_segs), block(VT / COLS, groups);
   for (int mode = seg_len ? 1 : 0; mode <= (seg_len ? 2 : 0); ++mode) {
     a.mode = mode;
-    launch_kernel(diag_scan_kernel<T, VT, FORM>, grid, block, smem, stream, a);
+    if (mode == 1)
+      launch_kernel(diag_scan_kernel<T, VT, FORM, true>, grid, block, smem, stream, a);
+    else
+      launch_kernel(diag_scan_kernel<T, VT, FORM, false>, grid, block, smem, stream, a);
     SCAN_CHECK("diag_scan");
     if (mode == 1) {
       const size_t per = (size_t)a.heads * a.dim * a.vdim;

@@ -112,8 +112,17 @@ class TimeMixWKV(Part):
         shift, S = view.state[:, :self.shift_cols], view.state[:, self.shift_cols:]
         mixes = ws.get("wkv_mixes", T, 5 * W, self.dtype)
         ops.token_shift(mixes, x, self.mu, shift, ctx)
-        rkvg = ws.get("wkv_rkvg", T, 4 * I, self.dtype)
-        ops.gemm_heads(mixes[:, :4 * W], self.w_rkvg, rkvg, T, 4)          # four products of four inputs in one launch
+        if (self.dtype == torch.bfloat16 and T < ops.NORMAL_MODE_FROM_ROWS
+                and all(ops.gemm_fast_available(mixes[:, m * W:], self.w_rkvg[m], None, T) for m in range(4))):
+            # few rows: the products are bound by the weights' bytes, which the tensor-core kernel of few rows streams with all
+            # SMs; one product per input, each into rows of its own (measured at width 2048, 64 requests: the per-head
+            # CUDA-core launch took 156 us, the four products take about 30)
+            r_, k_, v_, g_ = (linear(mixes[:, m * W:(m + 1) * W], self.w_rkvg[m], ws.get("wkv_" + "rkvg"[m], T, I, self.dtype), T)
+                              for m in range(4))
+        else:
+            rkvg = ws.get("wkv_rkvg", T, 4 * I, self.dtype)
+            ops.gemm_heads(mixes[:, :4 * W], self.w_rkvg, rkvg, T, 4)          # four products of four inputs in one launch
+            r_, k_, v_, g_ = (rkvg[:, m * I:(m + 1) * I] for m in range(4))
         low = linear(mixes[:, 4 * W:], self.w1, ws.get("wkv_low", T, R, self.dtype), T)
         low_t = ws.get("wkv_low_t", T, R, self.dtype)
         ops.act_rows(low_t, low, T, "tanh")
@@ -121,10 +130,10 @@ class TimeMixWKV(Part):
         z = linear(low_t, self.w2, ws.get("wkv_z", T, I, torch.float32), T)
         o = ws.get("wkv_o", T, I, torch.float32)
         seg, seg_state, seg_decay = _segments(ctx, "wkv", I * self.head_dim, I)
-        ops.wkv_scan(o, rkvg[:, :I], rkvg[:, I:2 * I], rkvg[:, 2 * I:3 * I], z, self.w0, self.bonus, S, ctx,
+        ops.wkv_scan(o, r_, k_, v_, z, self.w0, self.bonus, S, ctx,
                      shift_src=x, shift_state=shift, seg_len=seg, seg_state=seg_state, seg_decay=seg_decay)
         normed = ws.get("attn_out", T, I, self.dtype)
-        ops.group_rmsnorm_gate(normed, o, self.gain, rkvg[:, 3 * I:], T, self.num_heads, self.eps)
+        ops.group_rmsnorm_gate(normed, o, self.gain, g_, T, self.num_heads, self.eps)
         return linear(normed, self.w_o, ws.get("mixer_out", T, W, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 
