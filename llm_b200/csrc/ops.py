@@ -395,9 +395,10 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias, state:
                silu: bool = False) -> None:
     """out[t] = conv(x)_t (+ x_t if residual; silu of it if asked) over every entry's tokens, the entry's last taps - 1
     inputs before this step read from, and afterwards kept in, state [slots, >= (taps - 1) * channels] float32 (rows may be
-    strided: a column range of a wider state).  w float32 [channels, taps]; bias float32 [channels] or None."""
+    strided: a column range of a wider state).  w float32 [taps, channels] (a row per tap, the oldest input's first); bias
+    float32 [channels] or None."""
     _rows_contig(out, "out"); _rows_contig(x, "x"); _rows_contig(state, "state")
-    channels, taps = w.shape
+    taps, channels = w.shape
     assert x.shape[1] == out.shape[1] == channels and x.dtype == out.dtype
     assert w.dtype == torch.float32 and w.is_contiguous() and state.dtype == torch.float32
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == channels)

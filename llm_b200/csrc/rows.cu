@@ -670,6 +670,35 @@ __global__ void clamped_glu_kernel(T* __restrict__ out, MaybePartial<T> in, cons
   }
 }
 
+// The same, eight consecutive columns a thread with 16-byte accesses (inter a multiple of 8, aligned bases).
+template <typename T>
+__global__ void __launch_bounds__(256)
+clamped_glu_vec_kernel(T* __restrict__ out, MaybePartial<T> in, const float* __restrict__ bias, int inter, float limit,
+                       float alpha, size_t groups) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = inter / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / per_row, c = (i % per_row) * 8;
+    float g[8], u[8], y[8];
+    in.at8(r * 2 * inter + c, g);
+    in.at8(r * 2 * inter + inter + c, u);
+    if (bias) {
+      float bg[8], bu[8];
+      Vec8<float>::load(bias + c, bg);
+      Vec8<float>::load(bias + inter + c, bu);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { g[k] += bg[k]; u[k] += bu[k]; }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gg = fminf(g[k], limit), uu = fminf(fmaxf(u[k], -limit), limit);
+      y[k] = gg / (1.f + expf(-alpha * gg)) * (uu + 1.f);
+    }
+    Vec8<T>::store(out + r * inter + c, y);
+  }
+}
+
 LLMK_API int llmk_clamped_glu(void* out, const void* gate_up, const float* partials, int splits, long long split_stride,
                               const float* bias, int rows, int inter, float limit, float alpha, int dtype, cudaStream_t stream) {
   const long long total = (long long)rows * inter;
@@ -678,6 +707,14 @@ LLMK_API int llmk_clamped_glu(void* out, const void* gate_up, const float* parti
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> x{(const T*)gate_up, partials, splits, split_stride};
+    if (inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)partials % 16 == 0 &&
+        split_stride % 4 == 0 && (uintptr_t)bias % 16 == 0) {
+      long long vblocks = (total / 8 + 255) / 256;
+      if (vblocks > 65535 * 16) vblocks = 65535 * 16;
+      launch_kernel(clamped_glu_vec_kernel<T>, dim3((unsigned)vblocks), dim3(256), 0, stream, (T*)out, x, bias, inter, limit, alpha,
+                    (size_t)(total / 8));
+      LLMK_LAUNCH_CHECK("clamped_glu");
+    }
     long long blocks = (total + 255) / 256;
     if (blocks > 65535 * 16) blocks = 65535 * 16;
     launch_kernel(clamped_glu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, x, bias, inter, limit, alpha,

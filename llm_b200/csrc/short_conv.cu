@@ -37,11 +37,57 @@ short_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict
     if (src >= start) v = to_f32(x[(size_t)src * x_stride + c]);
     else v = st[(size_t)(taps - 1 + src - start) * channels + c];      // place k holds the input at start - (taps - 1) + k
     if (j == taps - 1) self = v;
-    y = fmaf(w[(size_t)c * taps + j], v, y);
+    y = fmaf(w[(size_t)j * channels + c], v, y);
   }
   if (residual) y += self;
   if (act) y = y / (1.f + expf(-y));
   out[(size_t)t * out_stride + c] = from_f32<T>(y);
+}
+
+// The same for eight channels a thread (16-byte accesses; channels a multiple of 8, at most TAPS taps) and `run` consecutive
+// tokens a thread, with the thread's weights in registers.  A token's rows are read again for the next token; they come
+// from the first-level cache.  The sums run over the taps in the same order as above.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128)
+short_conv_vec_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
+                      const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
+                      long long slot_stride, const int* __restrict__ state_slots, const int* __restrict__ token_entry,
+                      const int* __restrict__ cu_tokens, int n_tokens, int channels, int taps, int residual, int act, int run) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (c >= channels) return;
+  float wr[TAPS][8], b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = bias ? bias[c + i] : 0.f;
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) {
+    if (j < taps) Vec8<float>::load(w + (size_t)j * channels + c, wr[j]);
+  }
+  const int t_end = min(n_tokens, (int)(blockIdx.x + 1) * run);
+  for (int t = blockIdx.x * run; t < t_end; ++t) {
+    const int e = token_entry[t];
+    const int start = cu_tokens[e];
+    const float* st = state + (size_t)state_slots[e] * slot_stride;
+    float y[8], v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = b[i];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      if (j >= taps) break;
+      const int src = t - (taps - 1) + j;
+      if (src >= start) Vec8<T>::load(x + (size_t)src * x_stride + c, v);
+      else Vec8<float>::load(st + (size_t)(taps - 1 + src - start) * channels + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] = fmaf(wr[j][i], v[i], y[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {                    // v holds the token's own input (the last tap)
+      if (residual) y[i] += v[i];
+      if (act) y[i] = y[i] / (1.f + expf(-y[i]));
+    }
+    Vec8<T>::store(out + (size_t)t * out_stride + c, y);
+  }
 }
 
 template <typename T>
@@ -65,7 +111,7 @@ short_conv_state_kernel(const T* __restrict__ x, long long x_stride, float* __re
 
 }  // namespace
 
-// x, out [n_tokens, stride] (out may not be x); w float32 [channels, taps]; bias float32 [channels] or null;
+// x, out [n_tokens, stride] (out may not be x); w float32 [taps, channels] (a row per tap, oldest first); bias float32 [channels] or null;
 // state float32, slot s at state + s * slot_stride, [taps - 1, channels].
 LLMK_API int llmk_short_conv(void* out, long long out_stride, const void* x, long long x_stride, const float* w, const float* bias,
                              float* state, long long slot_stride, const int* state_slots, const int* token_entry,
@@ -78,9 +124,26 @@ LLMK_API int llmk_short_conv(void* out, long long out_stride, const void* x, lon
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     const unsigned bx = (unsigned)((channels + 255) / 256);
-    cudaError_t err = launch_kernel(short_conv_kernel<T>, dim3(n_tokens, bx), dim3(256), 0, stream, (T*)out, out_stride, (const T*)x,
-                                    x_stride, w, bias, (const float*)state, slot_stride, state_slots, token_entry, cu_tokens,
-                                    channels, taps, residual, act);
+    constexpr int per16 = 16 / (int)sizeof(T);
+    const bool vec = channels % 8 == 0 && taps <= 8 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0 && out_stride % per16 == 0 &&
+                     x_stride % per16 == 0 && (uintptr_t)state % 16 == 0 && slot_stride % 4 == 0 && (uintptr_t)w % 16 == 0;
+    cudaError_t err;
+    if (vec) {
+      const int run = n_tokens >= 4096 ? 8 : n_tokens >= 512 ? 4 : 1;      // long steps: a thread keeps its weights for some tokens
+      const dim3 grid((unsigned)((n_tokens + run - 1) / run), (unsigned)((channels / 8 + 127) / 128));
+      if (taps <= 4)
+        err = launch_kernel(short_conv_vec_kernel<T, 4>, grid, dim3(128), 0, stream, (T*)out, out_stride, (const T*)x, x_stride, w, bias,
+                            (const float*)state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
+                            act, run);
+      else
+        err = launch_kernel(short_conv_vec_kernel<T, 8>, grid, dim3(128), 0, stream, (T*)out, out_stride, (const T*)x, x_stride, w, bias,
+                            (const float*)state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
+                            act, run);
+    } else {
+      err = launch_kernel(short_conv_kernel<T>, dim3(n_tokens, bx), dim3(256), 0, stream, (T*)out, out_stride, (const T*)x,
+                          x_stride, w, bias, (const float*)state, slot_stride, state_slots, token_entry, cu_tokens,
+                          channels, taps, residual, act);
+    }
     if (err == cudaSuccess && taps > 1)
       launch_kernel(short_conv_state_kernel<T>, dim3(bx, n_entries), dim3(256), 0, stream, (const T*)x, x_stride, state,
                     slot_stride, state_slots, cu_tokens, channels, taps);

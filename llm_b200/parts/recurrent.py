@@ -173,7 +173,7 @@ class StateSpaceDuality(Part):
 
     def bind(self, tensors):
         t = lambda local: tensors[self.name(local)].contiguous()
-        self.w_in, self.w_conv, self.b_conv = t("in"), t("conv"), t("conv.b")
+        self.w_in, self.w_conv, self.b_conv = t("in"), t("conv").t().contiguous(), t("conv.b")      # [taps, channels]: a row per tap
         self.dt_bias, self.a_log, self.skip, self.gain, self.w_o = t("dt_bias"), t("A_log"), t("D"), t("norm"), t("o")
 
     def cache_need(self):
@@ -225,7 +225,7 @@ class ConvInput(Part):
         return {self.name(self.weight_name): ParamInfo((self.hidden_size, self.taps), kind="gain", init="normal")}
 
     def bind(self, tensors):
-        self.w = tensors[self.name(self.weight_name)].contiguous()
+        self.w = tensors[self.name(self.weight_name)].t().contiguous()            # [taps, width]: a row per tap
 
     def cache_need(self):
         return self.inner.cache_need()

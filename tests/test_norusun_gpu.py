@@ -113,7 +113,7 @@ def test_short_convolution_carries_its_inputs_between_steps(dtype, channels, tap
         rows = torch.cat([x[r][cuts[r][n][0]:cuts[r][n][1]] for r in live])
         ctx = step_ctx([cuts[r][n][1] - cuts[r][n][0] for r in live], [slot[r] for r in live])
         out = torch.empty(ctx.n_tokens, channels, device="cuda", dtype=DT[dtype])
-        ops.short_conv(out, dev(rows, dtype), dev(w), None if bias is None else dev(bias), state, ctx, residual=residual, silu=silu)
+        ops.short_conv(out, dev(rows, dtype), dev(w.T), None if bias is None else dev(bias), state, ctx, residual=residual, silu=silu)
         at = 0
         for r in live:
             k = cuts[r][n][1] - cuts[r][n][0]
