@@ -278,8 +278,8 @@ def test_clamped_gated_unit_cuts_all_three_ways(dtype, ff, rows, limit, alpha):
 # ---- whole models, every way of cutting the work --------------------------------------------
 # ---- prompt attention on the tensor cores with this design's options ----------------------------------------
 TC_OPTION_CASES = [  # heads, kv heads, head size, page, window or chunk, kind
-    (8, 1, 128, 16, 136, "sink"), (8, 1, 64, 32, 50, "sink"), (16, 1, 128, 64, 1, "sink"), (6, 1, 64, 16, 1000, "sink"),
-    (8, 4, 64, 16, 64, "sigmoid"), (4, 1, 128, 32, 200, "sigmoid"), (6, 6, 64, 16, 1, "sigmoid"), (8, 2, 128, 16, 37, "sigmoid"),
+    (4, 1, 128, 16, 150, "sink"), (8, 1, 64, 32, 50, "sink"), (16, 1, 128, 64, 1, "sink"), (6, 1, 64, 16, 1000, "sink"),
+    (12, 4, 64, 16, 48, "sigmoid"), (4, 1, 128, 32, 200, "sigmoid"), (6, 6, 64, 16, 1, "sigmoid"), (8, 2, 128, 16, 37, "sigmoid"),
     (4, 2, 64, 64, 0, "sigmoid"), (4, 2, 64, 16, 129, "chunk_softmax"),
 ]
 
