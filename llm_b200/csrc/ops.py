@@ -407,8 +407,8 @@ def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias, state:
                                   _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.token_entry),
                                   _ptr(ctx.cu_tokens), c_int(ctx.n_tokens), c_int(ctx.n_entries), c_int(channels), c_int(taps),
                                   c_int(int(residual)), c_int(int(silu)), c_int(_kind(x.dtype)), _stream()))
-    if taps > 1:
-        count_launches(1)
+    if taps > 1 and ctx.n_tokens != ctx.n_entries:
+        count_launches(1)            # the state's update is a launch of its own unless every entry brings one token
 
 
 # ---- recurrences with a diagonal decay (scan.cu) ------------------------------------------

@@ -8,7 +8,9 @@
 //
 // Two launches: the convolution (a thread per token and channel; it reads the old state), then the state's update
 // (a thread per entry and channel, which walks the taps - 1 places in ascending order: place k takes either an input of
-// this step or the old place k + n, which lies above every place written so far).
+// this step or the old place k + n, which lies above every place written so far).  When every entry brings one token
+// the convolution's thread is the only reader of its entry's places and moves them itself (place j - 1 takes what tap j
+// read): one launch.
 #include "common.cuh"
 
 namespace {
@@ -18,9 +20,9 @@ constexpr int MAX_TAPS = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
-                  const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
+                  const float* __restrict__ w, const float* __restrict__ bias, float* state,
                   long long slot_stride, const int* __restrict__ state_slots, const int* __restrict__ token_entry,
-                  const int* __restrict__ cu_tokens, int channels, int taps, int residual, int act) {
+                  const int* __restrict__ cu_tokens, int channels, int taps, int residual, int act, int single) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -28,7 +30,7 @@ short_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict
   if (c >= channels) return;
   const int e = token_entry[t];
   const int start = cu_tokens[e];
-  const float* st = state + (size_t)state_slots[e] * slot_stride;
+  float* st = state + (size_t)state_slots[e] * slot_stride;
   float y = bias ? bias[c] : 0.f;
   float self = 0.f;
   for (int j = 0; j < taps; ++j) {
@@ -37,6 +39,7 @@ short_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict
     if (src >= start) v = to_f32(x[(size_t)src * x_stride + c]);
     else v = st[(size_t)(taps - 1 + src - start) * channels + c];      // place k holds the input at start - (taps - 1) + k
     if (j == taps - 1) self = v;
+    if (single && j >= 1) st[(size_t)(j - 1) * channels + c] = v;
     y = fmaf(w[(size_t)j * channels + c], v, y);
   }
   if (residual) y += self;
@@ -50,9 +53,10 @@ short_conv_kernel(T* __restrict__ out, long long out_stride, const T* __restrict
 template <typename T, int TAPS>
 __global__ void __launch_bounds__(128)
 short_conv_vec_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ x, long long x_stride,
-                      const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
+                      const float* __restrict__ w, const float* __restrict__ bias, float* state,
                       long long slot_stride, const int* __restrict__ state_slots, const int* __restrict__ token_entry,
-                      const int* __restrict__ cu_tokens, int n_tokens, int channels, int taps, int residual, int act, int run) {
+                      const int* __restrict__ cu_tokens, int n_tokens, int channels, int taps, int residual, int act, int run,
+                      int single) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -68,7 +72,7 @@ short_conv_vec_kernel(T* __restrict__ out, long long out_stride, const T* __rest
   for (int t = blockIdx.x * run; t < t_end; ++t) {
     const int e = token_entry[t];
     const int start = cu_tokens[e];
-    const float* st = state + (size_t)state_slots[e] * slot_stride;
+    float* st = state + (size_t)state_slots[e] * slot_stride;
     float y[8], v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = b[i];
@@ -78,6 +82,7 @@ short_conv_vec_kernel(T* __restrict__ out, long long out_stride, const T* __rest
       const int src = t - (taps - 1) + j;
       if (src >= start) Vec8<T>::load(x + (size_t)src * x_stride + c, v);
       else Vec8<float>::load(st + (size_t)(taps - 1 + src - start) * channels + c, v);
+      if (single && j >= 1) Vec8<float>::store(st + (size_t)(j - 1) * channels + c, v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) y[i] = fmaf(wr[j][i], v[i], y[i]);
     }
@@ -128,23 +133,24 @@ LLMK_API int llmk_short_conv(void* out, long long out_stride, const void* x, lon
     const bool vec = channels % 8 == 0 && taps <= 8 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0 && out_stride % per16 == 0 &&
                      x_stride % per16 == 0 && (uintptr_t)state % 16 == 0 && slot_stride % 4 == 0 && (uintptr_t)w % 16 == 0;
     cudaError_t err;
+    const int single = n_tokens == n_entries;                  // every entry brings one token: the convolution moves the state
     if (vec) {
       const int run = n_tokens >= 4096 ? 8 : n_tokens >= 512 ? 4 : 1;      // long steps: a thread keeps its weights for some tokens
       const dim3 grid((unsigned)((n_tokens + run - 1) / run), (unsigned)((channels / 8 + 127) / 128));
       if (taps <= 4)
         err = launch_kernel(short_conv_vec_kernel<T, 4>, grid, dim3(128), 0, stream, (T*)out, out_stride, (const T*)x, x_stride, w, bias,
-                            (const float*)state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
-                            act, run);
+                            state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
+                            act, run, single);
       else
         err = launch_kernel(short_conv_vec_kernel<T, 8>, grid, dim3(128), 0, stream, (T*)out, out_stride, (const T*)x, x_stride, w, bias,
-                            (const float*)state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
-                            act, run);
+                            state, slot_stride, state_slots, token_entry, cu_tokens, n_tokens, channels, taps, residual,
+                            act, run, single);
     } else {
       err = launch_kernel(short_conv_kernel<T>, dim3(n_tokens, bx), dim3(256), 0, stream, (T*)out, out_stride, (const T*)x,
-                          x_stride, w, bias, (const float*)state, slot_stride, state_slots, token_entry, cu_tokens,
-                          channels, taps, residual, act);
+                          x_stride, w, bias, state, slot_stride, state_slots, token_entry, cu_tokens,
+                          channels, taps, residual, act, single);
     }
-    if (err == cudaSuccess && taps > 1)
+    if (err == cudaSuccess && taps > 1 && !single)
       launch_kernel(short_conv_state_kernel<T>, dim3(bx, n_entries), dim3(256), 0, stream, (const T*)x, x_stride, state,
                     slot_stride, state_slots, cu_tokens, channels, taps);
     LLMK_LAUNCH_CHECK("short_conv");
