@@ -23,6 +23,7 @@ class CacheInstance:
     head_dim: int
     values: bool = True       # False: keys and values are the same vectors; only one tensor of pages is kept
     value_dim: int = 0        # size of a value row (0: the same as a key row)
+    value_heads: int = 0      # value heads per token (0: as many as key heads)
 
 
 def element_size(dtype: torch.dtype) -> int:
@@ -31,7 +32,8 @@ def element_size(dtype: torch.dtype) -> int:
 
 def bytes_per_page(instances: List[CacheInstance], group: int, page_size: int, dtype: torch.dtype) -> int:
     """Bytes that one more page of this group costs over all its instances (K and V)."""
-    return sum(page_size * i.num_kv_heads * (i.head_dim + ((i.value_dim or i.head_dim) if i.values else 0)) * element_size(dtype)
+    return sum(page_size * (i.num_kv_heads * i.head_dim
+                            + ((i.value_heads or i.num_kv_heads) * (i.value_dim or i.head_dim) if i.values else 0)) * element_size(dtype)
                for i in instances if i.group == group)
 
 
@@ -48,7 +50,7 @@ class CacheStorage:
             shape = (pages_per_group[inst.group], inst.num_kv_heads, page_size, inst.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             # an instance without values hands out its key pages as value pages too
-            v_shape = shape[:3] + (inst.value_dim or inst.head_dim,)
+            v_shape = (shape[0], inst.value_heads or inst.num_kv_heads, page_size, inst.value_dim or inst.head_dim)
             self.v.append(torch.zeros(v_shape, dtype=dtype, device=device) if inst.values else self.k[-1])
 
     def pages(self, instance: int) -> Tuple[torch.Tensor, torch.Tensor]:

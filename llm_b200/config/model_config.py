@@ -413,6 +413,128 @@ class NorusunConfig:
 
 
 @dataclass(frozen=True)
+class PotipelConfig:
+    """config.json of a Potipel folder: a pre-norm decoder (RMS norms with a weight) whose `layers` list gives every layer
+    one by one, with a scaled embedding and a short causal convolution added to what every sublayer reads.  Keys:
+    `architecture`, `width`, `vocab`, `norm.eps`, `embedding.scale`, `canon.taps`, and per layer `type`, `mixer`, `mlp`
+    (`dense` with `ff`; `moe` with `expert.{ff, limit}` and `router.{experts, top, groups.{count, keep}}`; or null) and,
+    optionally, `weights_of`: the index of an earlier layer whose tensors this one uses, with a cache and state of its own.
+    Mixers:
+      attention  heads, kv_heads, dim, vdim, scale, diff                      (differential attention, two maps per head)
+      hgrn2      heads, dim, vdim
+      parallel   left  {heads, kv_heads, dim, vdim, scale, softcap, conv, mask.size}      (windowed attention with a sink)
+                 right {heads, kv_heads, dim, vdim, conv}                                  (gated delta rule)
+                 left_scale, right_scale
+    The design has no length limit of its own: max_position (optional) bounds what the engine sizes its tables for."""
+
+    architecture: str
+    width: int
+    vocab: int
+    norm_eps: float
+    embedding_scale: float
+    canon_taps: int
+    layers: tuple                      # of dicts, validated; "weights_of" is None or an index
+    max_position: int = 131072
+    eos_token_id: Optional[int] = None
+
+    MIXERS = ("attention", "hgrn2", "parallel")
+
+    @staticmethod
+    def _ints(d, keys, where):
+        out = {k: _take(d, k, int) for k in keys}
+        if min(out.values()) <= 0:
+            raise ConfigError(f"config.json: {where}: sizes must be positive")
+        return out
+
+    @classmethod
+    def _mixer(cls, kind: str, m: dict, where: str) -> dict:
+        if kind == "attention":
+            mixer = cls._ints(m, ("heads", "kv_heads", "dim", "vdim"), where)
+            mixer["scale"], mixer["diff"] = _take(m, "scale", float), _take(m, "diff", float)
+            if mixer["heads"] % mixer["kv_heads"]:
+                raise ConfigError(f"config.json: {where}: heads must be a multiple of kv_heads")
+            return mixer
+        if kind == "hgrn2":
+            return cls._ints(m, ("heads", "dim", "vdim"), where)
+        if kind == "parallel":
+            left, right = _take(m, "left", dict), _take(m, "right", dict)
+            a = cls._ints(left, ("heads", "kv_heads", "dim", "vdim", "conv"), where + ".left")
+            a["scale"], a["softcap"] = _take(left, "scale", float), _take(left, "softcap", float)
+            a["window"] = _take(_take(left, "mask", dict), "size", int)
+            b = cls._ints(right, ("heads", "kv_heads", "dim", "vdim", "conv"), where + ".right")
+            if a["heads"] % a["kv_heads"] or b["heads"] % b["kv_heads"] or a["window"] <= 0 or not a["softcap"] > 0:
+                raise ConfigError(f"config.json: {where}: heads must be a multiple of kv_heads, the window and the soft cap positive")
+            if max(a["conv"], b["conv"]) > 16:
+                raise ConfigError(f"config.json: {where}: a convolution has at most 16 taps")
+            return {"left": a, "right": b, "left_scale": _take(m, "left_scale", float), "right_scale": _take(m, "right_scale", float)}
+        raise ConfigError(f"config.json: {where[:-6]}.type '{kind}' is not a mixer of this design {cls.MIXERS}")
+
+    @staticmethod
+    def _mlp(ff, where: str):
+        if ff is None:
+            return None
+        if not isinstance(ff, dict):
+            raise ConfigError(f"config.json: {where} must be an object or null")
+        kind = _take(ff, "kind", str)
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": _take(ff, "ff", int)}
+            if mlp["ff"] <= 0:
+                raise ConfigError(f"config.json: {where}.ff must be positive")
+            return mlp
+        if kind == "moe":
+            expert, router = _take(ff, "expert", dict), _take(ff, "router", dict)
+            groups = _take(router, "groups", dict)
+            mlp = {"kind": "moe", "ff": _take(expert, "ff", int), "limit": _take(expert, "limit", float),
+                   "experts": _take(router, "experts", int), "top": _take(router, "top", int),
+                   "groups": _take(groups, "count", int), "keep": _take(groups, "keep", int)}
+            if mlp["ff"] <= 0 or not mlp["limit"] > 0 or not (0 < mlp["top"] <= mlp["experts"] <= 256):
+                raise ConfigError(f"config.json: {where}: ff and limit must be positive and 1 <= top <= experts <= 256")
+            if mlp["groups"] <= 0 or mlp["experts"] % mlp["groups"] or not (0 < mlp["keep"] <= mlp["groups"]) \
+                    or mlp["top"] > mlp["keep"] * (mlp["experts"] // mlp["groups"]):
+                raise ConfigError(f"config.json: {where}.router: {mlp['experts']} experts must divide into groups.count groups, "
+                                  f"1 <= keep <= count, and top fit into the kept groups")
+            return mlp
+        raise ConfigError(f"config.json: {where}.kind '{kind}' is not 'dense' or 'moe'")
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "PotipelConfig":
+        norm = _take(d, "norm", dict)
+        layers = _take(d, "layers", list)
+        if not layers:
+            raise ConfigError("config.json: 'layers' must list at least one layer")
+        out = []
+        for i, layer in enumerate(layers):
+            where = f"layers[{i}]"
+            if not isinstance(layer, dict):
+                raise ConfigError(f"config.json: {where} must be an object")
+            kind = _take(layer, "type", str)
+            entry = {"type": kind, "mixer": cls._mixer(kind, _take(layer, "mixer", dict), where + ".mixer"),
+                     "mlp": cls._mlp(layer.get("mlp"), where + ".mlp"), "weights_of": None}
+            src = layer.get("weights_of")
+            if src is not None:
+                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i) or out[src]["weights_of"] is not None:
+                    raise ConfigError(f"config.json: {where}.weights_of must name an earlier layer that has tensors of its own")
+                if {k: v for k, v in out[src].items() if k != "weights_of"} != {k: v for k, v in entry.items() if k != "weights_of"}:
+                    raise ConfigError(f"config.json: {where} uses the tensors of layer {src} but differs from it")
+                entry["weights_of"] = src
+            out.append(entry)
+        eos = d.get("eos_token_id")
+        cfg = cls(architecture=_take(d, "architecture", str), width=_take(d, "width", int), vocab=_take(d, "vocab", int),
+                  norm_eps=_take(norm, "eps", float), embedding_scale=_take(_take(d, "embedding", dict), "scale", float),
+                  canon_taps=_take(_take(d, "canon", dict), "taps", int), layers=tuple(out),
+                  max_position=_take(d, "max_position", int, 131072), eos_token_id=eos if isinstance(eos, int) else None)
+        if cfg.width <= 0 or cfg.vocab <= 0 or cfg.max_position <= 0:
+            raise ConfigError("config.json: width, vocab and max_position must be positive")
+        if not (1 <= cfg.canon_taps <= 16):
+            raise ConfigError("config.json: canon.taps must be 1 to 16")
+        return cfg
+
+    @property
+    def max_position_embeddings(self) -> int:
+        return self.max_position
+
+
+@dataclass(frozen=True)
 class Architecture:
     """One registry entry: how to read the config and how to lay the model out."""
 

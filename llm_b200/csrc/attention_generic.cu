@@ -74,7 +74,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
                                const int* __restrict__ positions, int n_tokens, int n_heads, int n_kv,
                                int head_dim, int vdim, int page_size, int window, int keep_first, float scale,
                                float softcap, int sink, bool vec, const float* __restrict__ sink_values, int chunk,
-                               const float* __restrict__ sigmoid_bias) {
+                               const float* __restrict__ sigmoid_bias, const float* __restrict__ dist_r1,
+                               const float* __restrict__ dist_r2, int v_share) {
   __shared__ float q_s[WARPS][MAXD];
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
@@ -89,6 +90,8 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
   const int keep_end = min(keep_first, lo);      // keys [0, keep_end) lie before the window and are seen all the same
   const int lo_tile = (lo / 32) * 32;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const float r1 = dist_r1 ? dist_r1[h] : 0.f, r2 = dist_r1 ? dist_r2[h] : 0.f;
+  const int n_v = n_kv / v_share, gv = g / v_share;      // v_share neighbouring key heads read one value head
 
   const T* q_row = q + (size_t)t * q_stride + (size_t)h * head_dim;
   for (int d = lane; d < head_dim; d += 32) q_s[warp][d] = to_f32(q_row[d]);
@@ -109,14 +112,15 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
     }
     const int kp = tile + lane;
     const bool valid = kp <= pos && (kp >= lo || kp < keep_end);
-    long long row = 0;                             // the key's place in units of rows: times head_dim or vdim
+    long long row = 0;                             // the value's place in units of rows of vdim
     float s = -INFINITY;
     if (valid) {
       const int page = table[kp / page_size];
-      row = ((long long)page * n_kv + g) * page_size + kp % page_size;
-      const T* k_row = k_pages + row * head_dim;
+      row = ((long long)page * n_v + gv) * page_size + kp % page_size;
+      const T* k_row = k_pages + (((long long)page * n_kv + g) * page_size + kp % page_size) * head_dim;
       s = (vec ? dot_row<T>(q_s[warp], k_row, head_dim) : dot_row_scalar<T>(q_s[warp], k_row, head_dim)) * scale;
       if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+      if (dist_r1) s -= r1 * log1pf(r2 * (float)(pos - kp));      // a bias that grows with the distance to the key
     }
     float p;
     if (gated) {
@@ -158,13 +162,19 @@ paged_attention_generic_kernel(T* __restrict__ out, long long out_stride, const 
 // q [n_tokens, q_stride] with head h at column h*head_dim; out [n_tokens, out_stride] with head h at column
 // h*vdim.  k_pages [pages, n_kv, page_size, head_dim], v_pages [pages, n_kv, page_size, vdim]; block_table [entries, table_width] holds,
 // for batch entry e, the page of positions [i*page_size, (i+1)*page_size) at column i.
-LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const void* q, long long q_stride,
-                                          const void* k_pages, const void* v_pages, const int* block_table,
-                                          int table_width, const int* token_entry, const int* positions,
-                                          int n_tokens, int n_heads, int n_kv, int head_dim, int vdim, int page_size,
-                                          int window, int keep_first, float scale, float softcap, int sink, int dtype,
-                                          cudaStream_t stream, const float* sink_values, int chunk, const float* sigmoid_bias) {
+// Further options: dist_r1, dist_r2 (float32 [heads], both or neither): r1[h] * ln(1 + r2[h] * (query position - key
+// position)) is taken off every score after the cap; v_share > 1: v_pages has n_kv / v_share heads and the key heads
+// v_share * i .. v_share * i + v_share - 1 read value head i (several attention maps over one set of values).
+LLMK_API int llmk_paged_attention_generic_ex(void* out, long long out_stride, const void* q, long long q_stride,
+                                             const void* k_pages, const void* v_pages, const int* block_table,
+                                             int table_width, const int* token_entry, const int* positions,
+                                             int n_tokens, int n_heads, int n_kv, int head_dim, int vdim, int page_size,
+                                             int window, int keep_first, float scale, float softcap, int sink, int dtype,
+                                             cudaStream_t stream, const float* sink_values, int chunk, const float* sigmoid_bias,
+                                             const float* dist_r1, const float* dist_r2, int v_share) {
   if (n_tokens == 0) return 0;
+  LLMK_REQUIRE(v_share >= 1 && n_kv % v_share == 0, "paged_attention: %d key heads do not share values in runs of %d", n_kv, v_share);
+  LLMK_REQUIRE((dist_r1 != nullptr) == (dist_r2 != nullptr), "paged_attention: the distance bias takes both of its numbers");
   LLMK_REQUIRE(head_dim > 0 && head_dim <= MAX_HEAD_DIM, "paged_attention: head_dim %d must be 1 to %d", head_dim, MAX_HEAD_DIM);
   LLMK_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "paged_attention: %d query heads do not divide into %d kv heads",
                n_heads, n_kv);
@@ -185,17 +195,28 @@ LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const
       launch_kernel(paged_attention_generic_kernel<T, 256>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias, dist_r1, dist_r2, v_share);
     else if (widest <= 512)      // the wide head of a latent attention (its rank)
       launch_kernel(paged_attention_generic_kernel<T, 512>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias, dist_r1, dist_r2, v_share);
     else
       launch_kernel(paged_attention_generic_kernel<T, MAX_HEAD_DIM>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (T*)out, out_stride, (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table,
           table_width, token_entry, positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
-          softcap, sink, vec, sink_values, chunk, sigmoid_bias);
+          softcap, sink, vec, sink_values, chunk, sigmoid_bias, dist_r1, dist_r2, v_share);
     LLMK_LAUNCH_CHECK("paged_attention_generic");
   });
+}
+
+LLMK_API int llmk_paged_attention_generic(void* out, long long out_stride, const void* q, long long q_stride,
+                                          const void* k_pages, const void* v_pages, const int* block_table,
+                                          int table_width, const int* token_entry, const int* positions,
+                                          int n_tokens, int n_heads, int n_kv, int head_dim, int vdim, int page_size,
+                                          int window, int keep_first, float scale, float softcap, int sink, int dtype,
+                                          cudaStream_t stream, const float* sink_values, int chunk, const float* sigmoid_bias) {
+  return llmk_paged_attention_generic_ex(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, token_entry,
+                                         positions, n_tokens, n_heads, n_kv, head_dim, vdim, page_size, window, keep_first, scale,
+                                         softcap, sink, dtype, stream, sink_values, chunk, sigmoid_bias, nullptr, nullptr, 1);
 }

@@ -27,7 +27,7 @@ GROUPS = {
     # group -> (library file, sources); runtime.cu (error text, switches) is linked into both
     "plain": (LIB_NAME, ["runtime.cu", "rows.cu", "gemm_simt.cu", "rope_cache.cu", "attention_generic.cu",
                          "attention_decode.cu", "sampling.cu", "latent.cu", "routed.cu", "recurrent.cu", "hyper.cu",
-                         "short_conv.cu", "scan.cu"]),
+                         "short_conv.cu", "scan.cu", "delta.cu"]),
     "tensor": ("libllm_b200_tensor.so", ["runtime.cu", "gemm_tc.cu", "attention_tc.cu", "attention_decode_mma.cu"]),
     # host side of the runtime (page pool, step metadata, scheduler): plain C++, built with g++, needs no CUDA
     "host": ("libllm_b200_host.so", ["host/page_pool.cpp", "host/scheduler.cpp"]),

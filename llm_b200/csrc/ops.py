@@ -116,13 +116,13 @@ def _rows_contig(t: torch.Tensor, name: str) -> None:
 
 
 def embedding(resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, n_tokens: int,
-              status: torch.Tensor) -> None:
-    """resid[:n_tokens] (float32) = table[ids]; an id outside the table sets status[0]."""
+              status: torch.Tensor, scale: float = 1.0) -> None:
+    """resid[:n_tokens] (float32) = table[ids] * scale; an id outside the table sets status[0]."""
     assert resid.dtype == torch.float32 and ids.dtype == torch.int32 and status.dtype == torch.int32
     assert resid.is_contiguous() and table.is_contiguous()
     vocab, hidden = table.shape
-    _check(load().llmk_embedding(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens), c_int(hidden),
-                                 c_int(vocab), c_int(_kind(table.dtype)), _ptr(status), _stream()))
+    _check(load().llmk_embedding_scaled(_ptr(resid), _ptr(table), _ptr(ids), c_int(n_tokens), c_int(hidden),
+                                        c_int(vocab), c_int(_kind(table.dtype)), _ptr(status), c_float(scale), _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, gamma: torch.Tensor, out, rows: int, eps: float) -> None:
@@ -389,6 +389,67 @@ def scalar_rmsnorm_rows(out: torch.Tensor, x: torch.Tensor, gain: torch.Tensor, 
                                            c_int(_kind(out.dtype)), _stream()))
 
 
+def diff_combine(out: torch.Tensor, a: torch.Tensor, gate, rows: int, heads: int, per_group: int, lam: float, post: float,
+                 eps: float) -> None:
+    """Two attention maps per head combined: a [rows, 2 * heads * V] holds the maps' outputs ordered [kv group][map][head
+    within the group]; out[t, h] = rms_unit(a1 - lam * a2) * post * sigmoid(gate[t, h]) (gate in out's dtype, rows may be
+    strided, or None), heads in their own order."""
+    _rows_contig(a, "a")
+    vdim = out.shape[-1] // heads
+    assert out.is_contiguous() and out.dtype == a.dtype and a.shape[1] == 2 * heads * vdim and heads % per_group == 0
+    if gate is not None:
+        _rows_contig(gate, "gate")
+        assert gate.dtype == out.dtype and gate.shape[1] == heads * vdim
+    _check(load().llmk_diff_combine(_ptr(out), _ptr(a), c_longlong(a.stride(0)), _ptr(gate),
+                                    c_longlong(gate.stride(0) if gate is not None else 0), c_int(rows), c_int(heads),
+                                    c_int(per_group), c_int(vdim), c_float(lam), c_float(post), c_float(eps),
+                                    c_int(_kind(out.dtype)), _stream()))
+
+
+def scaled_sum(out: torch.Tensor, a, b, sa: float, sb: float, rows: int) -> None:
+    """out[:rows] = sa * a + sb * b; a and b tensors or PartialSums [rows, width]."""
+    width = out.shape[-1]
+    assert out.is_contiguous()
+    for t in (a, b):
+        if isinstance(t, PartialSum):
+            assert t.cols == width and t.rows == rows
+        else:
+            assert t.is_contiguous() and t.shape[-1] == width and t.dtype == out.dtype
+    da, pa, sa_, sta = _split_args(a)
+    db, pb, sb_, stb = _split_args(b)
+    _check(load().llmk_scaled_sum(_ptr(out), da, pa, sa_, sta, db, pb, sb_, stb, c_float(sa), c_float(sb), c_int(rows),
+                                  c_int(width), c_int(_kind(out.dtype)), _stream()))
+
+
+def head_norm_kv_write(qkv, q_gain, k_gain, eps: float, slot_map, k_pages, v_pages, n_tokens: int, n_q: int, n_k: int, n_v: int,
+                       dim: int, vdim: int, q_out=None) -> torch.Tensor:
+    """A row of n_q query heads and n_k key heads of dim, then n_v value heads of vdim (a tensor or a PartialSum): every q
+    and k head is RMS-normed on its own with one shared weight (q_gain, k_gain float32 [dim]; None: not normed); q goes to
+    q_out (the source itself for a tensor unless given), k and v to slot_map in pages of n_k and n_v heads.  Returns q."""
+    width = (n_q + n_k) * dim + n_v * vdim
+    if isinstance(qkv, PartialSum):
+        assert q_out is not None and qkv.cols >= width
+        src_stride = qkv.cols
+    else:
+        _rows_contig(qkv, "qkv")
+        assert qkv.shape[1] >= width
+        src_stride = qkv.stride(0)
+        if q_out is None:
+            q_out = qkv
+    _rows_contig(q_out, "q_out")
+    assert q_out.dtype == qkv.dtype and slot_map.dtype == torch.int32
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype == qkv.dtype
+    assert k_pages.shape[1] == n_k and k_pages.shape[3] == dim and v_pages.shape[1] == n_v and v_pages.shape[3] == vdim
+    for t in (q_gain, k_gain):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == dim)
+    d, parts, splits, stride = _split_args(qkv)
+    _check(load().llmk_head_norm_kv_write(d, parts, splits, stride, c_longlong(src_stride), _ptr(q_out), c_longlong(q_out.stride(0)),
+                                          _ptr(q_gain), _ptr(k_gain), c_float(eps), _ptr(slot_map), _ptr(k_pages), _ptr(v_pages),
+                                          c_int(n_tokens), c_int(n_q), c_int(n_k), c_int(n_v), c_int(dim), c_int(vdim),
+                                          c_int(k_pages.shape[2]), c_int(_kind(qkv.dtype)), _stream()))
+    return q_out
+
+
 # ---- short convolution (short_conv.cu) ----------------------------------------------------
 
 def short_conv(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias, state: torch.Tensor, ctx, residual: bool = False,
@@ -487,6 +548,47 @@ def ssd_scan(out: torch.Tensor, x: torch.Tensor, b: torch.Tensor, c: torch.Tenso
                                 *_segment_scratch(ctx, seg_len, seg_state, seg_decay, heads * dim * vdim, heads * dim)))
     if seg_len:
         count_launches(2)
+
+
+def gate_scan(out: torch.Tensor, q: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias, lower: torch.Tensor,
+              state: torch.Tensor, ctx, heads: int, dim: int, vdim: int, seg_len: int = 0, seg_state=None, seg_decay=None) -> None:
+    """S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t), f_t = lower + (1 - lower) sigmoid(z_t + z_bias)
+    per head (scan.cu).  q [T, heads*dim], v [T, heads*vdim] in the compute dtype; z float32 [T, heads*dim]; z_bias, lower
+    float32 [heads*dim]; state float32 [slots, >= heads*dim*vdim]; out float32 [T, heads*vdim].  Segments as in wkv_scan."""
+    for t in (out, q, v, z, state):
+        _rows_contig(t, "gate_scan operand")
+    assert q.dtype == v.dtype and q.shape[1] == z.shape[1] == heads * dim and v.shape[1] == out.shape[1] == heads * vdim
+    assert z.dtype == out.dtype == state.dtype == lower.dtype == torch.float32 and lower.numel() == heads * dim
+    assert z_bias is None or (z_bias.dtype == torch.float32 and z_bias.numel() == heads * dim)
+    assert state.shape[1] >= heads * dim * vdim
+    _check(load().llmk_gate_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(v),
+                                 c_longlong(v.stride(0)), _ptr(z), c_longlong(z.stride(0)), _ptr(z_bias), _ptr(lower), _ptr(state),
+                                 c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.cu_tokens), c_int(ctx.n_entries),
+                                 c_int(heads), c_int(dim), c_int(vdim), c_int(_kind(q.dtype)), _stream(), c_int(ctx.n_tokens),
+                                 c_int(seg_len), *_segment_scratch(ctx, seg_len, seg_state, seg_decay, heads * dim * vdim, heads * dim)))
+    if seg_len:
+        count_launches(2)
+
+
+def delta_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: torch.Tensor, a: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, ctx, heads: int, qk_heads: int, dim: int,
+               vdim: int, q_scale: float, norm_eps: float = 1e-6) -> None:
+    """The gated delta rule (delta.cu): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per head, with q and k
+    made unit vectors per head (q also times q_scale), beta = sigmoid(b), g = exp(-exp(a_log) softplus(a + dt_bias)).
+    q, k [T, qk_heads*dim] (equal row strides), v [T, heads*vdim], b, a [T, heads] (equal row strides), all in the compute
+    dtype; a_log, dt_bias float32 [heads]; state float32 [slots, >= heads*dim*vdim]; out float32 [T, heads*vdim]."""
+    for t in (out, q, k, v, b, a, state):
+        _rows_contig(t, "delta_scan operand")
+    assert q.stride(0) == k.stride(0) and b.stride(0) == a.stride(0) and q.dtype == k.dtype == v.dtype == b.dtype == a.dtype
+    assert q.shape[1] == k.shape[1] == qk_heads * dim and v.shape[1] == out.shape[1] == heads * vdim
+    assert b.shape[1] == a.shape[1] == heads and out.dtype == state.dtype == torch.float32 and state.shape[1] >= heads * dim * vdim
+    for t in (a_log, dt_bias):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads
+    _check(load().llmk_delta_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(q), _ptr(k), c_longlong(q.stride(0)), _ptr(v),
+                                  c_longlong(v.stride(0)), _ptr(b), _ptr(a), c_longlong(b.stride(0)), _ptr(a_log), _ptr(dt_bias),
+                                  _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots), _ptr(ctx.cu_tokens),
+                                  c_int(ctx.n_entries), c_int(heads), c_int(qk_heads), c_int(dim), c_int(vdim), c_float(q_scale),
+                                  c_float(norm_eps), c_int(_kind(q.dtype)), _stream()))
 
 
 def group_rmsnorm_gate(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, rows: int, groups: int,
@@ -610,7 +712,7 @@ def moe_max_tiles(n_pairs: int, experts: int, tile: int = 0) -> int:
 
 
 def moe_route(h: torch.Tensor, w: torch.Tensor, bias, logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-              n_tokens: int, top: int, over_all: bool = False) -> None:
+              n_tokens: int, top: int, over_all: bool = False, sigmoid_groups=None) -> None:
     """Router (over_all: the weights are the chosen experts' shares of the softmax over all experts, not
     renormalised): logits = h @ w.T with float32 accumulation (the tensor-core product in bfloat16 where it takes the
     shape, the CUDA-core product otherwise) into `logits` (float32 [>= n_tokens, experts]); plus bias, the `top`
@@ -627,6 +729,12 @@ def moe_route(h: torch.Tensor, w: torch.Tensor, bias, logits: torch.Tensor, ids:
         gemm_simt(h, w, logits, n_tokens)
         z = logits
     d, parts, splits, stride = _split_args(z)
+    if sigmoid_groups is not None:
+        # (groups, keep): sigmoid scores, `bias` is the correction that enters the choice only; see routed.cu
+        groups, keep = sigmoid_groups
+        _check(load().llmk_moe_topk_sigmoid(d, parts, splits, stride, _ptr(bias), _ptr(ids), _ptr(weights), c_int(n_tokens),
+                                            c_int(experts), c_int(top), c_int(groups), c_int(keep), _stream()))
+        return
     _check(load().llmk_moe_topk(d, parts, splits, stride, _ptr(bias), _ptr(ids), _ptr(weights), c_int(n_tokens),
                                 c_int(experts), c_int(top), c_int(int(over_all)), _stream()))
 
@@ -719,8 +827,11 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor, rows: int) -> None:
                                 c_int(_kind(x.dtype)), _stream()))
 
 
-def silu_mul(out: torch.Tensor, gate_up, rows: int) -> None:
-    """out[:rows, :I] = silu(gate_up[:, :I]) * gate_up[:, I:]; gate_up a tensor or a PartialSum."""
+GLU_ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def silu_mul(out: torch.Tensor, gate_up, rows: int, act: str = "silu") -> None:
+    """out[:rows, :I] = act(gate_up[:, :I]) * gate_up[:, I:] with act silu or relu; gate_up a tensor or a PartialSum."""
     inter = out.shape[-1]
     assert out.is_contiguous() and out.dtype == gate_up.dtype
     if isinstance(gate_up, PartialSum):
@@ -728,8 +839,8 @@ def silu_mul(out: torch.Tensor, gate_up, rows: int) -> None:
     else:
         assert gate_up.shape[-1] == 2 * inter and gate_up.is_contiguous()
     d, parts, splits, stride = _split_args(gate_up)
-    _check(load().llmk_silu_mul(_ptr(out), d, parts, splits, stride, c_int(rows), c_int(inter),
-                                c_int(_kind(out.dtype)), _stream()))
+    _check(load().llmk_glu_mul(_ptr(out), d, parts, splits, stride, c_int(rows), c_int(inter),
+                               c_int(_kind(out.dtype)), c_int(GLU_ACTIVATIONS[act]), _stream()))
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> None:
@@ -780,25 +891,30 @@ def paged_attention_generic(out: torch.Tensor, q: torch.Tensor, k_pages: torch.T
                             block_table: torch.Tensor, token_entry: torch.Tensor, positions: torch.Tensor,
                             n_tokens: int, n_heads: int, n_kv: int, head_dim: int, window: int,
                             scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
-                            keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None) -> None:
+                            keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None, dist_bias=None,
+                            v_share: int = 1) -> None:
     """out[t, h*VS:(h+1)*VS] = causal (windowed) attention of q[t, h] over its request's pages.  value_dim: size of a
     value row where it differs from the keys' (0 = the same); softcap > 0: scores pass cap * tanh(s / cap); sink: the
     softmax's denominator gets one more term of score 0, or of score sink_values[h] (float32 [heads], not scaled);
     keep_first: with a window, the request's first keys stay visible; chunk > 0: instead of a window, a query sees the
     keys at or before it with the same floor(position / chunk); sigmoid_bias (float32 [heads]): the weight of a visible
-    key is sigmoid(score + bias[h]) and nothing is normalised."""
-    for t in (sink_values, sigmoid_bias):
+    key is sigmoid(score + bias[h]) and nothing is normalised.  dist_bias (r1, r2), float32 [heads] each:
+    r1[h] * ln(1 + r2[h] * distance) is taken off the capped score.  v_share > 1: v_pages holds n_kv / v_share heads and
+    v_share neighbouring key heads read one of them."""
+    r1, r2 = dist_bias if dist_bias is not None else (None, None)
+    for t in (sink_values, sigmoid_bias, r1, r2):
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+    assert v_share >= 1 and k_pages.shape[1] == n_kv and v_pages.shape[1] * v_share == n_kv
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert token_entry.dtype == torch.int32 and positions.dtype == torch.int32
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and q.dtype == k_pages.dtype == out.dtype
-    _check(load().llmk_paged_attention_generic(
+    _check(load().llmk_paged_attention_generic_ex(
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(token_entry), _ptr(positions), c_int(n_tokens),
         c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(value_dim or head_dim), c_int(k_pages.shape[2]), c_int(window or 0),
         c_int(keep_first or 0), c_float(scale), c_float(softcap or 0.0), c_int(int(bool(sink))), c_int(_kind(q.dtype)), _stream(),
-        _ptr(sink_values), c_int(chunk or 0), _ptr(sigmoid_bias)))
+        _ptr(sink_values), c_int(chunk or 0), _ptr(sigmoid_bias), _ptr(r1), _ptr(r2), c_int(v_share)))
 
 
 def feed_tokens(token_ids: torch.Tensor, sampled: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, n: int) -> None:
@@ -964,7 +1080,8 @@ def attention_tc_take_error() -> int:
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
                     window: int, scale: float, value_dim: int = 0, softcap: float = 0.0, sink: bool = False,
-                    keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None) -> None:
+                    keep_first: int = 0, sink_values=None, chunk: int = 0, sigmoid_bias=None, dist_bias=None,
+                    v_share: int = 1) -> None:
     """Attention of the step's tokens over their requests' pages; q is the first
     n_heads * head_dim columns of qkv.  Chooses the kernel for the batch: in bfloat16 the
     split-key decode kernel when every entry brings one token and the tcgen05 kernel otherwise,
@@ -972,7 +1089,15 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     off the 16-grid among them).  value_dim, softcap, sink, keep_first: see paged_attention_generic, the kernel
     that takes them in every combination.  sink_values (a learned score per head for the sink), chunk and sigmoid_bias (a
     chunked mask, sigmoid weights): the tcgen05 kernel for steps with prompt portions where it takes the sizes; else the
-    split-key decode kernel (sink_values) or the general kernel, whose one warp per (token, head) walks at most one chunk."""
+    split-key decode kernel (sink_values) or the general kernel, whose one warp per (token, head) walks at most one chunk.
+    dist_bias (a bias that grows with the logarithm of the distance) and v_share (several key heads over one value head):
+    the general kernel."""
+    if dist_bias is not None or v_share > 1:
+        paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
+                                ctx.n_tokens, n_heads, n_kv, head_dim, window, scale, value_dim=value_dim,
+                                softcap=softcap, sink=sink or sink_values is not None, keep_first=keep_first,
+                                sink_values=sink_values, dist_bias=dist_bias, v_share=v_share)
+        return
     if chunk or sigmoid_bias is not None:
         if (not ctx.decode_only and not softcap and (not value_dim or value_dim == head_dim) and qkv.stride(0) % 8 == 0
                 and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):

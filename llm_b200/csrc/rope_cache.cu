@@ -241,6 +241,45 @@ norm_rope_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restri
   }
 }
 
+// ---- norm per head with one shared weight, store; k and v with head counts of their own ----------------------
+// A row holds n_q query heads and n_k key heads of dim numbers, then n_v value heads of vdim.  Every q and k head is
+// divided by its own root mean square (eps inside the root) and multiplied by gain [dim], one weight vector for all of them
+// (null: the heads pass as they are); q goes to q_out, k and v to the token's slot in their pages, which may hold different
+// numbers of heads (several attention maps over one set of values).  A warp per head; sums in float32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_kv_write_kernel(MaybePartial<T> src, long long src_stride, T* __restrict__ q_out, long long q_out_stride,
+                          const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                          const int* __restrict__ slot_map, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q, int n_k,
+                          int n_v, int dim, int vdim, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const size_t row = (size_t)t * src_stride;
+  size_t page = 0, off = 0;
+  if (n_k || n_v) {
+    const int slot = slot_map[t];
+    page = slot / page_size; off = slot % page_size;
+  }
+  for (int head = warp; head < n_q + n_k; head += warps) {
+    const bool is_q = head < n_q;
+    const float* gain = is_q ? q_gain : k_gain;
+    const size_t c0 = row + (size_t)head * dim;
+    float ss = 0.f;
+    if (gain)
+      for (int d = lane; d < dim; d += 32) { const float v = src.at(c0 + d); ss = fmaf(v, v, ss); }
+    const float r = gain ? 1.f / sqrtf(warp_sum(ss) / (float)dim + eps) : 1.f;
+    T* dst = is_q ? q_out + (size_t)t * q_out_stride + (size_t)head * dim
+                  : k_pages + ((page * n_k + (head - n_q)) * page_size + off) * dim;
+    for (int d = lane; d < dim; d += 32) dst[d] = from_f32<T>(gain ? src.at(c0 + d) * r * gain[d] : src.at(c0 + d));
+  }
+  const size_t v0 = row + (size_t)(n_q + n_k) * dim;
+  for (int idx = threadIdx.x; idx < n_v * vdim; idx += blockDim.x) {
+    const int g = idx / vdim, d = idx % vdim;
+    v_pages[((page * n_v + g) * page_size + off) * vdim + d] = from_f32<T>(src.at(v0 + idx));
+  }
+}
+
 }  // namespace
 
 // qkv / partials as in llmk_rope_kv_write; q_out may be the source itself (a pair is read and written by
@@ -287,5 +326,24 @@ LLMK_API int llmk_norm_rope_kv_write(const void* qkv, const float* partials, int
                   q_out_stride, q_gain, k_gain, eps, freqs, rot_pairs, halves, positions, slot_map, (T*)k_pages, (T*)v_pages,
                   n_heads, n_kv, dim, vdim, page_size);
     LLMK_LAUNCH_CHECK("norm_rope_kv_write");
+  });
+}
+
+// qkv / partials as in llmk_rope_kv_write: a row of n_q * dim | n_k * dim | n_v * vdim numbers.  q_gain, k_gain float32
+// [dim] (null: no norm on that side); k_pages [pages, n_k, page_size, dim], v_pages [pages, n_v, page_size, vdim].
+LLMK_API int llmk_head_norm_kv_write(const void* qkv, const float* partials, int splits, long long split_stride,
+                                     long long src_stride, void* q_out, long long q_out_stride, const float* q_gain,
+                                     const float* k_gain, float eps, const int* slot_map, void* k_pages, void* v_pages,
+                                     int n_tokens, int n_q, int n_k, int n_v, int dim, int vdim, int page_size, int dtype,
+                                     cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE((qkv != nullptr) != (partials != nullptr), "head_norm_kv_write: give qkv or partials");
+  LLMK_REQUIRE(n_q >= 0 && n_k >= 0 && n_v >= 0 && dim > 0 && vdim > 0 && page_size > 0, "head_norm_kv_write: bad sizes");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> src{(const T*)qkv, partials, splits, split_stride};
+    launch_kernel(head_norm_kv_write_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, src, src_stride, (T*)q_out, q_out_stride,
+                  q_gain, k_gain, eps, slot_map, (T*)k_pages, (T*)v_pages, n_q, n_k, n_v, dim, vdim, page_size);
+    LLMK_LAUNCH_CHECK("head_norm_kv_write");
   });
 }

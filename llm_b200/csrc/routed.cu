@@ -82,6 +82,81 @@ topk_kernel(MaybePartial<float> z, const float* __restrict__ bias, int* __restri
   }
 }
 
+// Sigmoid router with groups: scores s = sigmoid(z); the choice is made on s + correction, the weights are the chosen
+// experts' s themselves (not renormalised).  The experts form `groups` equal runs of neighbours; a group's score is the sum
+// of its two largest choice scores (of its one, in groups of one), and only experts of the `keep` best groups can be chosen:
+// the others are struck out (minus infinity, since choice scores may be negative).  Ties go to the lower index, for groups
+// and for experts.  One warp per token.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+topk_sigmoid_kernel(MaybePartial<float> z, const float* __restrict__ correction, int* __restrict__ ids,
+                    float* __restrict__ weights, int n_tokens, int experts, int top, int groups, int keep) {
+  __shared__ float c_s[ROUTE_WARPS][MAX_EXPERTS], s_s[ROUTE_WARPS][MAX_EXPERTS], g_s[ROUTE_WARPS][MAX_EXPERTS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
+  for (int e = lane; e < experts; e += 32) {
+    const float sc = 1.f / (1.f + expf(-z.at((size_t)t * experts + e)));
+    s_s[warp][e] = sc;
+    c_s[warp][e] = sc + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (keep < groups) {
+    const int per = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;               // the largest and the second largest of the group
+      for (int i = 0; i < per; ++i) {
+        const float v = c_s[warp][g * per + i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      g_s[warp][g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // strike out every group but the `keep` best: keep rounds of arg-max mark a group with +infinity
+    for (int j = 0; j < keep; ++j) {
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = g_s[warp][g];
+        if (v != INFINITY && v > best) { best = v; arg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ov > best || (ov == best && oa < arg)) { best = ov; arg = oa; }
+      }
+      if (lane == 0 && arg < groups) g_s[warp][arg] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (g_s[warp][e / per] != INFINITY) c_s[warp][e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = c_s[warp][e];
+      if (v > best) { best = v; arg = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ov > best || (ov == best && oa < arg)) { best = ov; arg = oa; }
+    }
+    if (lane == 0) {
+      const bool found = arg < experts;
+      ids[(size_t)t * top + j] = found ? arg : -1;              // nothing left to choose: the pair is dropped
+      weights[(size_t)t * top + j] = found ? s_s[warp][arg] : 0.f;
+      if (found) c_s[warp][arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
 // One block.  counts -> padded offsets -> slots.  meta[0] = tiles in use.
 __global__ void __launch_bounds__(1024)
 group_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ meta, int* __restrict__ tile_expert,
@@ -282,6 +357,23 @@ LLMK_API int llmk_moe_topk(const float* logits, const float* partials, int split
   launch_kernel(topk_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, bias, ids,
                 weights, n_tokens, experts, top, over_all);
   LLMK_LAUNCH_CHECK("moe_topk");
+}
+
+// The sigmoid router with groups (see topk_sigmoid_kernel): correction float32 [experts] or null; groups divides experts;
+// 1 <= keep <= groups.
+LLMK_API int llmk_moe_topk_sigmoid(const float* logits, const float* partials, int splits, long long split_stride,
+                                   const float* correction, int* ids, float* weights, int n_tokens, int experts, int top,
+                                   int groups, int keep, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  LLMK_REQUIRE((logits != nullptr) != (partials != nullptr), "moe_topk_sigmoid: give logits or partials");
+  LLMK_REQUIRE(experts > 0 && experts <= MAX_EXPERTS, "moe_topk_sigmoid: %d experts (1 to %d)", experts, MAX_EXPERTS);
+  LLMK_REQUIRE(top > 0 && top <= experts, "moe_topk_sigmoid: top %d of %d experts", top, experts);
+  LLMK_REQUIRE(groups > 0 && experts % groups == 0 && keep > 0 && keep <= groups,
+               "moe_topk_sigmoid: %d experts in %d groups of which %d are kept", experts, groups, keep);
+  MaybePartial<float> z{logits, partials, splits, split_stride};
+  launch_kernel(topk_sigmoid_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z,
+                correction, ids, weights, n_tokens, experts, top, groups, keep);
+  LLMK_LAUNCH_CHECK("moe_topk_sigmoid");
 }
 
 // ids [n_pairs] -> meta[0] (tiles in use), tile_expert [max_tiles], slot_src [max_tiles * 64] (the pair of

@@ -11,7 +11,7 @@
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ resid, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab,
-                                 int* __restrict__ status) {
+                                 int* __restrict__ status, float scale) {
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
   const int t = blockIdx.x;
@@ -22,17 +22,24 @@ __global__ void embedding_kernel(float* __restrict__ resid, const T* __restrict_
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) resid[(size_t)t * hidden + c] = to_f32(row[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) resid[(size_t)t * hidden + c] = to_f32(row[c]) * scale;
+}
+
+// scale: every row is multiplied by it in float32 on its way into the stream (1 = the plain copy).
+LLMK_API int llmk_embedding_scaled(float* resid, const void* table, const int* ids, int n_tokens, int hidden,
+                                   int vocab, int dtype, int* status, float scale, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, resid, (const T*)table, ids, hidden, vocab, status,
+                  scale);
+    LLMK_LAUNCH_CHECK("embedding");
+  });
 }
 
 LLMK_API int llmk_embedding(float* resid, const void* table, const int* ids, int n_tokens, int hidden,
                             int vocab, int dtype, int* status, cudaStream_t stream) {
-  if (n_tokens == 0) return 0;
-  return dispatch_dtype(dtype, [&](auto* tag) {
-    using T = LLMK_ELEM(tag);
-    launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, resid, (const T*)table, ids, hidden, vocab, status);
-    LLMK_LAUNCH_CHECK("embedding");
-  });
+  return llmk_embedding_scaled(resid, table, ids, n_tokens, hidden, vocab, dtype, status, 1.f, stream);
 }
 
 // ---- residual add + RMSNorm -------------------------------------------------
@@ -203,7 +210,7 @@ LLMK_API int llmk_add_bias(void* x, long long stride, const float* bias, int row
 // in [rows, 2*inter]: gate in the first half of a row, up in the second.
 // act = g / (1 + exp(-g)) * u in float32 (kernel/activation/SwiGLU.h:31-33).
 template <typename T, bool VEC>
-__global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int inter, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int inter, size_t total, int relu) {
   pdl_launch_dependents();      // let the next kernel start its own prologue now
   pdl_wait();
   if (VEC) {
@@ -216,7 +223,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int int
       in.at8(r * 2 * inter + c, g);
       in.at8(r * 2 * inter + inter + c, u);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+      for (int k = 0; k < 8; ++k) g[k] = (relu ? fmaxf(g[k], 0.f) : g[k] / (1.0f + expf(-g[k]))) * u[k];
       Vec8<T>::store(out + r * inter + c, g);
     }
     return;
@@ -225,15 +232,17 @@ __global__ void silu_mul_kernel(T* __restrict__ out, MaybePartial<T> in, int int
     const size_t r = i / inter, c = i % inter;
     const float g = in.at(r * 2 * inter + c);
     const float u = in.at(r * 2 * inter + inter + c);
-    out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    out[i] = from_f32<T>((relu ? fmaxf(g, 0.f) : g / (1.0f + expf(-g))) * u);
   }
 }
 
-LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials, int splits,
-                           long long split_stride, int rows, int inter, int dtype, cudaStream_t stream) {
+// act 0: silu(gate) * up; 1: relu(gate) * up.
+LLMK_API int llmk_glu_mul(void* out, const void* gate_up, const float* partials, int splits,
+                          long long split_stride, int rows, int inter, int dtype, int act, cudaStream_t stream) {
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
-  LLMK_REQUIRE((gate_up != nullptr) != (partials != nullptr), "silu_mul: give gate_up or partials");
+  LLMK_REQUIRE((gate_up != nullptr) != (partials != nullptr), "glu_mul: give gate_up or partials");
+  LLMK_REQUIRE(act == 0 || act == 1, "glu_mul: activation %d is not silu (0) or relu (1)", act);
   return dispatch_dtype(dtype, [&](auto* tag) {
     using T = LLMK_ELEM(tag);
     MaybePartial<T> in{(const T*)gate_up, partials, splits, split_stride};
@@ -241,11 +250,16 @@ LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials
     size_t blocks = ((vec ? total / 8 : total) + 255) / 256;
     if (blocks > (size_t)llmk_sm_count() * 32) blocks = (size_t)llmk_sm_count() * 32;
     if (vec)
-      launch_kernel(silu_mul_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
+      launch_kernel(silu_mul_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total, act);
     else
-      launch_kernel(silu_mul_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total);
+      launch_kernel(silu_mul_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, in, inter, total, act);
     LLMK_LAUNCH_CHECK("silu_mul");
   });
+}
+
+LLMK_API int llmk_silu_mul(void* out, const void* gate_up, const float* partials, int splits,
+                           long long split_stride, int rows, int inter, int dtype, cudaStream_t stream) {
+  return llmk_glu_mul(out, gate_up, partials, splits, split_stride, rows, inter, dtype, 0, stream);
 }
 
 // ---- residual add + Dynamic Tanh ----------------------------------------------
@@ -649,6 +663,81 @@ LLMK_API int llmk_head_rmsnorm_gate(void* out, const float* x, const float* w, c
     launch_kernel(head_rmsnorm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, x, w,
                   (const T*)gate, gate_stride, items, heads, vdim, eps);
     LLMK_LAUNCH_CHECK("head_rmsnorm_gate");
+  });
+}
+
+// ---- two attention maps combined per head ---------------------------------------------
+// Differential attention's output stage.  a holds 2 * heads attention outputs of vdim per token, ordered by kv group:
+// [group][map][head within the group] (the order in which grouped-query attention takes the query heads when each map's
+// keys are a kv head of their own).  Per head: o = a1 - lambda * a2, o / sqrt(mean(o^2) + eps) * post, times
+// sigmoid(gate) if a gate is given; out [t, heads * vdim] in the heads' own order.  A warp per (t, head); float32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(T* __restrict__ out, const T* __restrict__ a, long long a_stride, const T* __restrict__ gate,
+                    long long gate_stride, long long items, int heads, int per_group, int vdim, float lambda, float post,
+                    float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const long long t = item / heads;
+  const int h = (int)(item % heads);
+  const int first = (h / per_group) * 2 * per_group + h % per_group;
+  const T* a1 = a + (size_t)t * a_stride + (size_t)first * vdim;
+  const T* a2 = a1 + (size_t)per_group * vdim;
+  float ss = 0.f;
+  for (int c = lane; c < vdim; c += 32) {
+    const float o = fmaf(-lambda, to_f32(a2[c]), to_f32(a1[c]));
+    ss = fmaf(o, o, ss);
+  }
+  const float r = post / sqrtf(warp_sum(ss) / (float)vdim + eps);
+  const T* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * vdim : nullptr;
+  for (int c = lane; c < vdim; c += 32) {
+    float y = fmaf(-lambda, to_f32(a2[c]), to_f32(a1[c])) * r;
+    if (g) y *= 1.f / (1.f + expf(-to_f32(g[c])));
+    out[(size_t)item * vdim + c] = from_f32<T>(y);
+  }
+}
+
+LLMK_API int llmk_diff_combine(void* out, const void* a, long long a_stride, const void* gate, long long gate_stride,
+                               int n_tokens, int heads, int per_group, int vdim, float lambda, float post, float eps,
+                               int dtype, cudaStream_t stream) {
+  const long long items = (long long)n_tokens * heads;
+  if (items == 0) return 0;
+  LLMK_REQUIRE(per_group > 0 && heads % per_group == 0 && vdim > 0, "diff_combine: %d heads in groups of %d", heads, per_group);
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    launch_kernel(diff_combine_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (T*)out, (const T*)a,
+                  a_stride, (const T*)gate, gate_stride, items, heads, per_group, vdim, lambda, post, eps);
+    LLMK_LAUNCH_CHECK("diff_combine");
+  });
+}
+
+// ---- a scaled sum of two rows ---------------------------------------------------------
+// out = sa * a + sb * b row by row (two mixers side by side); a and b tensors or split-K partial results.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scaled_sum_kernel(T* __restrict__ out, MaybePartial<T> a, MaybePartial<T> b, float sa, float sb, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(fmaf(sa, a.at(i), sb * b.at(i)));
+}
+
+LLMK_API int llmk_scaled_sum(void* out, const void* a, const float* a_parts, int a_splits, long long a_stride, const void* b,
+                             const float* b_parts, int b_splits, long long b_stride, float sa, float sb, int rows, int width,
+                             int dtype, cudaStream_t stream) {
+  const size_t total = (size_t)rows * width;
+  if (total == 0) return 0;
+  LLMK_REQUIRE((a != nullptr) != (a_parts != nullptr) && (b != nullptr) != (b_parts != nullptr), "scaled_sum: give each side as a tensor or as partials");
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    using T = LLMK_ELEM(tag);
+    MaybePartial<T> ma{(const T*)a, a_parts, a_splits, a_stride}, mb{(const T*)b, b_parts, b_splits, b_stride};
+    size_t blocks = (total + 255) / 256;
+    if (blocks > (size_t)llmk_sm_count() * 32) blocks = (size_t)llmk_sm_count() * 32;
+    launch_kernel(scaled_sum_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (T*)out, ma, mb, sa, sb, total);
+    LLMK_LAUNCH_CHECK("scaled_sum");
   });
 }
 

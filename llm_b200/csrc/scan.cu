@@ -5,6 +5,9 @@
 //   scalar form (state-space duality):     S_t = a_t S_{t-1} + dt_t B_t x_t^T,          y_t = S_t^T C_t + D x_t
 //                                          dt_t = softplus(dt'_t + dt_bias),  a_t = exp(-exp(A_log) dt_t)   per head;
 //                                          B and C are shared by the heads of a group
+//   gate form (HGRN2):                     S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,   o_t = S_t^T silu(q_t)
+//                                          f_t = l + (1 - l) sigmoid(z_t + b)   per head and key channel, l a lower bound:
+//                                          what the forget gate lets go is what is written, so there is no key
 //
 // S [dim, vdim] is float32 and lives in the request's state slot (zero at admission); it is read at the start of an
 // entry's tokens and written back at their end, so prompts, portions and single tokens run the same arithmetic.  Decays,
@@ -27,7 +30,7 @@
 namespace {
 
 constexpr int ROWS = 8, COLS = 4, CHUNK = 8, MAX_GROUPS = 32;
-enum : int { FORM_BONUS = 0, FORM_SCALAR = 1 };
+enum : int { FORM_BONUS = 0, FORM_SCALAR = 1, FORM_GATE = 2 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -36,7 +39,7 @@ struct ScanArgs {
   const void *q, *k, *v; long long qk_stride, v_stride;      // q, k: [T, qk_heads * dim]; v: [T, heads * vdim]
   const float* z; long long z_stride;            // bonus form: the decay's pre-activation [T, heads * dim] float32
   const float* z_bias;                           // bonus form: w0 [heads * dim]
-  const float* bonus;                            // bonus form: u [heads, dim]
+  const float* bonus;                            // bonus form: u [heads, dim]; gate form: the lower bound l [heads, dim]
   const void* dt; long long dt_stride;           // scalar form: dt' [T, heads]
   const float *dt_bias, *a_log, *skip;           // scalar form: [heads] each
   float* state; long long slot_stride;           // slot s at state + s * slot_stride: [heads, dim, vdim]
@@ -116,7 +119,8 @@ diag_scan_kernel(ScanArgs a) {
   const bool v_regs = CHUNK * VT <= VREGS * nthreads;       // else (fewer than 32 channels) the values are read when staged
   T q_r[CHUNK], k_r[CHUNK], v_r[VREGS], dt_r;
   float z_r[CHUNK];
-  const float zb = (FORM == FORM_BONUS && tid < dim) ? a.z_bias[head * dim + tid] : 0.f;
+  const float zb = (FORM != FORM_SCALAR && tid < dim && a.z_bias) ? a.z_bias[head * dim + tid] : 0.f;
+  const float low = (FORM == FORM_GATE && tid < dim) ? a.bonus[head * dim + tid] : 0.f;
   auto fetch = [&](int c0) {
     const int n = min(CHUNK, t1 - c0);
 #pragma unroll
@@ -124,8 +128,8 @@ diag_scan_kernel(ScanArgs a) {
       if (c < n && tid < dim) {
         const size_t at = (size_t)(c0 + c) * a.qk_stride + (size_t)qk_head * dim + tid;
         if (!STATE_ONLY) q_r[c] = q[at];
-        k_r[c] = k[at];
-        if (FORM == FORM_BONUS) z_r[c] = a.z[(size_t)(c0 + c) * a.z_stride + (size_t)head * dim + tid];
+        if (FORM != FORM_GATE) k_r[c] = k[at];
+        if (FORM != FORM_SCALAR) z_r[c] = a.z[(size_t)(c0 + c) * a.z_stride + (size_t)head * dim + tid];
       }
     }
     if (v_regs) {
@@ -152,15 +156,21 @@ diag_scan_kernel(ScanArgs a) {
       float qv = 0.f, kv = 0.f, av = 0.f;
       if (tid < dim) {
         if (!STATE_ONLY) qv = to_f32(q_r[c]);
-        kv = to_f32(k_r[c]);
-        if (FORM == FORM_BONUS)
-          av = expf(-expf(z_r[c] + zb));
-        else
-          kv *= a_s[c];                       // dt B
+        if (FORM == FORM_GATE) {
+          if (!STATE_ONLY) qv = qv / (1.f + expf(-qv));
+          av = low + (1.f - low) / (1.f + expf(-(z_r[c] + zb)));
+          kv = 1.f - av;
+        } else {
+          kv = to_f32(k_r[c]);
+          if (FORM == FORM_BONUS)
+            av = expf(-expf(z_r[c] + zb));
+          else
+            kv *= a_s[c];                       // dt B
+        }
       }
       if (!STATE_ONLY) q_s[c * dpad + tid] = qv;
       k_s[c * dpad + tid] = kv;
-      if (FORM == FORM_BONUS) a_s[c * dpad + tid] = av;
+      if (FORM != FORM_SCALAR) a_s[c * dpad + tid] = av;
     }
     if (v_regs) {
 #pragma unroll
@@ -189,7 +199,7 @@ diag_scan_kernel(ScanArgs a) {
           const float4 q4 = *reinterpret_cast<const float4*>(q_s + c * dpad + g * ROWS + r);
           qc[r] = q4.x; qc[r + 1] = q4.y; qc[r + 2] = q4.z; qc[r + 3] = q4.w;
         }
-        if (FORM == FORM_BONUS) {
+        if (FORM != FORM_SCALAR) {
           const float4 a4 = *reinterpret_cast<const float4*>(a_s + c * dpad + g * ROWS + r);
           ac[r] = a4.x; ac[r + 1] = a4.y; ac[r + 2] = a4.z; ac[r + 3] = a4.w;
         } else {
@@ -450,6 +460,25 @@ LLMK_API int llmk_ssd_scan(float* out, long long out_stride, const void* x, long
   a.dim = dim; a.vdim = vdim;
   return dispatch_dtype(dtype, [&](auto* tag) {
     return launch_scan<LLMK_ELEM(tag), FORM_SCALAR>(a, n_entries, n_tokens, seg_len, seg_state, seg_decay, stream);
+  });
+}
+
+// The gate form.  q [T, heads * dim] (silu is taken here) and v [T, heads * vdim] in the projections' kind with row strides of
+// their own; z float32 [T, heads * dim] the forget gate's pre-activation, z_bias and lower float32 [heads * dim].
+LLMK_API int llmk_gate_scan(float* out, long long out_stride, const void* q, long long q_stride, const void* v, long long v_stride,
+                            const float* z, long long z_stride, const float* z_bias, const float* lower, float* state,
+                            long long slot_stride, const int* state_slots, const int* cu_tokens, int n_entries, int heads, int dim,
+                            int vdim, int dtype, cudaStream_t stream, int n_tokens, int seg_len, float* seg_state,
+                            float* seg_decay) {
+  if (n_entries == 0) return 0;
+  LLMK_REQUIRE(dim > 0 && dim <= ROWS * MAX_GROUPS, "gate_scan: key size %d (1 to %d)", dim, ROWS * MAX_GROUPS);
+  LLMK_REQUIRE(lower != nullptr && z != nullptr, "gate_scan: the gate's pre-activation and its lower bound are needed");
+  ScanArgs a = {};
+  a.out = out; a.out_stride = out_stride; a.q = q; a.k = nullptr; a.v = v; a.qk_stride = q_stride; a.v_stride = v_stride;
+  a.z = z; a.z_stride = z_stride; a.z_bias = z_bias; a.bonus = lower; a.state = state; a.slot_stride = slot_stride;
+  a.state_slots = state_slots; a.cu_tokens = cu_tokens; a.heads = a.qk_heads = heads; a.dim = dim; a.vdim = vdim;
+  return dispatch_dtype(dtype, [&](auto* tag) {
+    return launch_scan<LLMK_ELEM(tag), FORM_GATE>(a, n_entries, n_tokens, seg_len, seg_state, seg_decay, stream);
   });
 }
 

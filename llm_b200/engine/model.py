@@ -47,7 +47,9 @@ class Model:
             layer = spec.layers[layer_idx]
             mixer = getattr(self.blocks[layer_idx], "mixer", None)      # a block without a mixer keeps nothing
             need: Optional[CacheNeed] = mixer.cache_need() if mixer is not None else None
-            state: Optional[StateNeed] = mixer.state_need() if mixer is not None else None
+            block = self.blocks[layer_idx]             # a block may keep more than its mixer does (a feed-forward with state)
+            state: Optional[StateNeed] = (block.state_need() if hasattr(block, "state_need")
+                                          else mixer.state_need() if mixer is not None else None)
             inst, owns = None, True
             if layer.cache_of is not None:
                 if need is not None:
@@ -63,7 +65,7 @@ class Model:
                     self.group_keys.append(key)
                 inst = len(self.cache_instances)
                 self.cache_instances.append(CacheInstance(self.group_keys.index(key), need.num_kv_heads, need.head_dim, need.values,
-                                                          need.value_dim or need.head_dim))
+                                                          need.value_dim or need.head_dim, need.value_heads or 0))
                 latest[layer_idx] = inst
             st = None
             if state is not None:

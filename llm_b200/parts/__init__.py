@@ -1,4 +1,4 @@
-from . import (attention, block, embedding, feed_forward, gla, hyper, latent_attention, norm, position, recurrent,  # noqa: F401
+from . import (attention, block, diff_attention, embedding, feed_forward, gla, hyper, latent_attention, norm, position, recurrent,  # noqa: F401
                routed)  # noqa: F401 (register kinds)
 from .base import (CacheNeed, ParamInfo, Part, ResidualStream, StateNeed, build_part, part_class,
                    register_part)

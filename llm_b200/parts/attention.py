@@ -17,7 +17,11 @@ pairs of channels (kind "rope_pairs"); other tensor names.  Further: an RMS norm
 whole k projection, before they are split into heads and before rotation (qk_norm="whole", weights `q.norm`, `k.norm`);
 a mask by chunks (a query sees the keys at or before it whose position has the same floor(position / chunk), chunks
 counted from the request's first token); and sigmoid weights, sigmoid(score + b_h) with a learned number per head and
-no normalisation over the keys (weights="sigmoid").
+no normalisation over the keys (weights="sigmoid").  Further still: a sink whose score is a learned number per head
+(sink="learned", tensor `sink`); a bias that grows with the distance, r1_h ln(1 + r2_h (i - j)) taken off the capped score
+(dist_bias, tensors `r1`, `r2`); a short causal convolution over time on every channel of the projected (and biased) q, k, v
+(qkv_conv = taps, tensors `<projection>.conv` [channels, taps]; the last taps - 1 projected rows are the request's state); and
+biases on q, k, v without one on the output (out_bias=False).
 """
 from __future__ import annotations
 
@@ -26,11 +30,13 @@ import math
 import torch
 
 from ..csrc import ops
-from .base import CacheNeed, ParamInfo, Part, build_part, register_part
+from .base import CacheNeed, ParamInfo, Part, StateNeed, build_part, register_part
 from .linear import FUSE_PARTIALS, linear
 
 
-_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+          "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias",
+          "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "sink": "sink", "r1": "r1", "r2": "r2"}
 
 
 class PagedAttention(Part):
@@ -39,7 +45,8 @@ class PagedAttention(Part):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position=None,
                  window=None, scale=None, shares_cache: bool = False, bias: bool = False, value_dim=None, softcap=None,
                  sink: bool = False, keep_first: int = 0, names=None, chunk=None, weights: str = "softmax", qk_norm=None,
-                 norm_eps: float = 1e-6, prefix: str = "", dtype=None, device=None):
+                 norm_eps: float = 1e-6, out_bias=None, qkv_conv: int = 0, dist_bias: bool = False, prefix: str = "",
+                 dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         if num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} heads do not divide into {num_kv_heads} kv heads")
@@ -53,6 +60,13 @@ class PagedAttention(Part):
         self.value_dim = int(value_dim) if value_dim else head_dim
         self.softcap = float(softcap) if softcap else 0.0
         self.sink, self.keep_first = bool(sink), int(keep_first or 0)
+        self.learned_sink = sink == "learned"
+        self.dist_bias, self.qkv_conv = bool(dist_bias), int(qkv_conv or 0)
+        if not (0 <= self.qkv_conv <= 16):
+            raise ValueError(f"attention: a convolution of {qkv_conv} taps (0 to 16)")
+        if (self.qkv_conv or self.dist_bias or self.learned_sink) and (shares_cache or position is not None):
+            raise ValueError("attention: the convolution, the distance bias and the learned sink go with a cache of the "
+                             "layer's own and no position part")
         if self.keep_first and not self.window:
             self.keep_first = 0                   # without a window every token is seen anyway
         self.names = dict(_NAMES, **(names or {}))
@@ -66,10 +80,13 @@ class PagedAttention(Part):
             raise ValueError("attention: sigmoid weights take no sink and no soft cap")
         # the options above, and pair rotation, run on the path that rotates and stores with one kernel and
         # attends with a kernel that takes them (see forward)
-        self.extended = bool(self.value_dim != head_dim or self.softcap or self.sink or self.keep_first
-                             or self.chunk or self.sigmoid or self.qk_norm or (self.position is not None and hasattr(self.position, "frequencies")))
-        if self.extended and (bias or (self.position is not None and not hasattr(self.position, "frequencies"))):
-            raise ValueError("attention: value_dim, softcap, sink and keep_first go with pair rotation or no positions, without biases")
+        self.extended = bool(self.value_dim != head_dim or self.softcap or self.sink or self.keep_first or self.qkv_conv
+                             or self.dist_bias or self.chunk or self.sigmoid or self.qk_norm
+                             or (self.position is not None and hasattr(self.position, "frequencies")))
+        self.out_bias = bool(bias) if out_bias is None else bool(out_bias)
+        if self.extended and ((bias and self.out_bias) or (self.position is not None and not hasattr(self.position, "frequencies"))):
+            raise ValueError("attention: value_dim, softcap, sink and keep_first go with pair rotation or no positions, "
+                             "without a bias on the output")
         self.q_size = num_heads * head_dim
         self.kv_size = 0 if shares_cache else num_kv_heads * head_dim
         self.v_size = 0 if shares_cache else num_kv_heads * self.value_dim
@@ -79,6 +96,8 @@ class PagedAttention(Part):
         self.b_qkv = None
         self.b_o = None
         self.score_bias = self.q_gain = self.k_gain = None
+        self.sink_values = self.r1 = self.r2 = self.w_conv = None
+        self.conv_cols = (max(self.qkv_conv - 1, 0) * (self.q_size + self.kv_size + self.v_size) + 3) // 4 * 4
 
     def parameters(self):
         n = lambda k: self.name(self.names[k])
@@ -94,11 +113,20 @@ class PagedAttention(Part):
             if not self.shares_cache:
                 p[self.name(self.names.get("k_norm", "k.norm"))] = ParamInfo((self.kv_size,), kind="gain", init="ones_normal")
         if self.bias:
-            p[self.name("q_proj.bias")] = ParamInfo((self.q_size,), kind="gain", init="normal")
+            p[n("q_bias")] = ParamInfo((self.q_size,), kind="gain", init="normal")
             if not self.shares_cache:
-                p[self.name("k_proj.bias")] = ParamInfo((self.kv_size,), kind="gain", init="normal")
-                p[self.name("v_proj.bias")] = ParamInfo((self.kv_size,), kind="gain", init="normal")
-            p[self.name("o_proj.bias")] = ParamInfo((self.hidden_size,), kind="gain", init="normal")
+                p[n("k_bias")] = ParamInfo((self.kv_size,), kind="gain", init="normal")
+                p[n("v_bias")] = ParamInfo((self.v_size,), kind="gain", init="normal")
+            if self.out_bias:
+                p[n("o_bias")] = ParamInfo((self.hidden_size,), kind="gain", init="normal")
+        if self.learned_sink:
+            p[n("sink")] = ParamInfo((self.num_heads,), kind="gain", init="normal")
+        if self.dist_bias:
+            p[n("r1")] = ParamInfo((self.num_heads,), kind="gain", init="normal")
+            p[n("r2")] = ParamInfo((self.num_heads,), kind="gain", init="ones_normal")
+        if self.qkv_conv:
+            for m, c in (("q_conv", self.q_size), ("k_conv", self.kv_size), ("v_conv", self.v_size)):
+                p[n(m)] = ParamInfo((c, self.qkv_conv), kind="gain", init="normal")
         return p
 
     def bind(self, tensors):
@@ -115,9 +143,15 @@ class PagedAttention(Part):
             if not self.shares_cache:
                 self.k_gain = tensors[self.name(self.names.get("k_norm", "k.norm"))].contiguous()
         if self.bias:
-            names = ["q_proj.bias"] + ([] if self.shares_cache else ["k_proj.bias", "v_proj.bias"])
-            self.b_qkv = torch.cat([tensors[self.name(n)] for n in names]).contiguous()
-            self.b_o = tensors[self.name("o_proj.bias")].contiguous()
+            names = ["q_bias"] + ([] if self.shares_cache else ["k_bias", "v_bias"])
+            self.b_qkv = torch.cat([n(m) for m in names]).contiguous()
+            self.b_o = n("o_bias").contiguous() if self.out_bias else None
+        if self.learned_sink:
+            self.sink_values = n("sink").contiguous()
+        if self.dist_bias:
+            self.r1, self.r2 = n("r1").contiguous(), n("r2").contiguous()
+        if self.qkv_conv:
+            self.w_conv = torch.cat([n("q_conv"), n("k_conv"), n("v_conv")], dim=0).t().contiguous()      # [taps, channels]
 
     def cache_need(self):
         if self.shares_cache:
@@ -128,7 +162,8 @@ class PagedAttention(Part):
                          value_dim=self.value_dim, keep_first=self.keep_first)
 
     def state_need(self):
-        return None
+        # the convolution over the projected rows keeps the request's last taps - 1 of them
+        return StateNeed((max(self.conv_cols, 4),), torch.float32) if self.qkv_conv else None
 
     def children(self):
         return [self.position] if self.position is not None else []
@@ -206,7 +241,11 @@ class PagedAttention(Part):
         k_pages, v_pages = view.k_pages, view.v_pages
         n_kv = k_pages.shape[1]
         qkv = linear(x, self.w_qkv, ws.get("qkv", T, self.q_size + self.kv_size + self.v_size, self.dtype), T,
-                     allow_partial=FUSE_PARTIALS)
+                     allow_partial=FUSE_PARTIALS, bias=self.b_qkv)
+        if self.qkv_conv:      # directly behind the (biased) projection; the request's last rows come from its state
+            conv = ws.get("qkv_conv", T, qkv.shape[1], self.dtype)
+            ops.short_conv(conv, qkv, self.w_conv, None, view.state, ctx)
+            qkv = conv
         freqs = self.position.frequencies() if self.position is not None else None
         halves = getattr(self.position, "layout", "pairs") == "halves"
         q_out = ws.get("q_rot", T, self.q_size, self.dtype) if isinstance(qkv, ops.PartialSum) else None
@@ -220,7 +259,8 @@ class PagedAttention(Part):
         attn = ws.get("attn_out", T, H * V, self.dtype)
         ops.paged_attention(attn, q, k_pages, v_pages, view.group, ctx, H, n_kv, D, self.window or 0, self.scale,
                             value_dim=V, softcap=self.softcap, sink=self.sink, keep_first=self.keep_first,
-                            chunk=self.chunk, sigmoid_bias=self.score_bias)
+                            chunk=self.chunk, sigmoid_bias=self.score_bias, sink_values=self.sink_values,
+                            dist_bias=(self.r1, self.r2) if self.dist_bias else None)
         return linear(attn, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
 
 

@@ -71,6 +71,8 @@ class CacheNeed:
     values: bool = True       # False: one vector per token serves as key and as value (a latent), so no value pages exist
     value_dim: Optional[int] = None     # size of a value row where it differs from a key row's
     keep_first: int = 0       # with a window: the request's first tokens stay visible after the window has passed them
+    value_heads: Optional[int] = None   # value heads per token where they are fewer than the key heads (several attention
+                                        # maps, each with keys of its own, over one set of values)
 
     def group_key(self):
         return (self.kind, self.window, self.keep_first)

@@ -7,7 +7,11 @@ out norm2 and ffn: it is x += mixer(norm1(x)) alone.
 """
 from __future__ import annotations
 
-from .base import ResidualStream, build_part, register_part
+import dataclasses
+
+import torch
+
+from .base import ResidualStream, StateNeed, build_part, register_part
 
 
 class PreNormBlock:
@@ -23,11 +27,35 @@ class PreNormBlock:
                       for r in self.roles}
         self.norm1, self.mixer = self.parts["norm1"], self.parts["mixer"]
         self.norm2, self.ffn = self.parts["norm2"], self.parts["ffn"]
+        # a feed-forward that keeps something per request (the inputs of a convolution over time) says so with state_need();
+        # the layer's state row is then the mixer's numbers followed by the feed-forward's
+        self.ffn_state = self.ffn.state_need() if self.ffn is not None and hasattr(self.ffn, "state_need") else None
+        self.mixer_cols = 0
+        if self.ffn_state is not None:
+            need = self.mixer.state_need()
+            n = 1
+            for d in (need.shape if need is not None else (0,)):
+                n *= int(d)
+            self.mixer_cols = (n + 3) // 4 * 4
+            if need is not None and need.dtype != torch.float32 or self.ffn_state.dtype != torch.float32 or len(self.ffn_state.shape) != 1:
+                raise ValueError("prenorm block: the states of a mixer and a feed-forward that share a row are flat float32")
+
+    def state_need(self):
+        """What the layer keeps per request: the mixer's state, followed by the feed-forward's where it has one."""
+        if self.ffn_state is None:
+            return self.mixer.state_need()
+        return StateNeed((self.mixer_cols + int(self.ffn_state.shape[0]),), torch.float32)
 
     def forward(self, stream: ResidualStream, ctx, view) -> None:
-        stream.pending = self.mixer.forward(self.norm1.forward(stream, ctx), ctx, view)
-        if self.ffn is not None:
-            stream.pending = self.ffn.forward(self.norm2.forward(stream, ctx), ctx)
+        if self.ffn_state is None:
+            stream.pending = self.mixer.forward(self.norm1.forward(stream, ctx), ctx, view)
+            if self.ffn is not None:
+                stream.pending = self.ffn.forward(self.norm2.forward(stream, ctx), ctx)
+            return
+        rows = view.state.view(view.state.shape[0], -1)
+        mixer_view = dataclasses.replace(view, state=rows[:, :self.mixer_cols] if self.mixer_cols else None)
+        stream.pending = self.mixer.forward(self.norm1.forward(stream, ctx), ctx, mixer_view)
+        stream.pending = self.ffn.forward(self.norm2.forward(stream, ctx), ctx, state=rows[:, self.mixer_cols:])
 
 
 register_part("block", "prenorm", PreNormBlock)

@@ -17,10 +17,13 @@ from .linear import linear
 class TokenEmbedding(Part):
     role = "embedding"
 
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", copies: int = 1, prefix: str = "",
-                 dtype=None, device=None):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight", copies: int = 1, scale: float = 1.0,
+                 prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.scale = float(scale)             # every row is multiplied by it (float32) on its way into the stream
+        if self.scale != 1.0 and int(copies) > 1:
+            raise ValueError("token embedding: a scale goes with one copy of the stream")
         self.copies = int(copies)             # a stream kept as several copies: each starts as the embedding
         self.weight_name = weight_name        # "": the table is the tensor named like the part
         self.table = None
@@ -35,7 +38,7 @@ class TokenEmbedding(Part):
         if self.copies > 1:
             ops.hc_embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, self.copies, ctx.status)
         else:
-            ops.embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, ctx.status)
+            ops.embedding(stream.resid, self.table, ctx.token_ids, ctx.n_tokens, ctx.status, self.scale)
         stream.pending = stream.pending_post = None
 
 

@@ -14,12 +14,22 @@ from .base import ParamInfo, Part, register_part
 from .linear import FUSE_PARTIALS, linear, linear_act, linear_swiglu
 
 
+_GLU_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight",
+              "gate_bias": "gate_proj.bias", "up_bias": "up_proj.bias", "down_bias": "down_proj.bias"}
+
+
 class SwiGLU(Part):
+    """down( act(gate(x)) * up(x) ) with act silu (the default) or relu; other tensor names through `names`."""
+
     role = "ffn"
 
-    def __init__(self, hidden_size: int, intermediate_size: int, bias: bool = False, prefix: str = "", dtype=None,
-                 device=None):
+    def __init__(self, hidden_size: int, intermediate_size: int, bias: bool = False, activation: str = "silu", names=None,
+                 prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
+        if activation not in ops.GLU_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: unknown activation '{activation}'; known: {sorted(ops.GLU_ACTIVATIONS)}")
+        self.activation = activation
+        self.names = dict(_GLU_NAMES, **(names or {}))
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.bias = bool(bias)        # the three projections carry bias vectors (model/modules/MLP.h:9-13)
         self.w_gate_up = None
@@ -28,32 +38,34 @@ class SwiGLU(Part):
         self.b_down = None
 
     def parameters(self):
+        n = lambda k: self.name(self.names[k])
         p = {
-            self.name("gate_proj.weight"): ParamInfo((self.intermediate_size, self.hidden_size)),
-            self.name("up_proj.weight"): ParamInfo((self.intermediate_size, self.hidden_size)),
-            self.name("down_proj.weight"): ParamInfo((self.hidden_size, self.intermediate_size)),
+            n("gate"): ParamInfo((self.intermediate_size, self.hidden_size)),
+            n("up"): ParamInfo((self.intermediate_size, self.hidden_size)),
+            n("down"): ParamInfo((self.hidden_size, self.intermediate_size)),
         }
         if self.bias:
-            p[self.name("gate_proj.bias")] = ParamInfo((self.intermediate_size,), kind="gain", init="normal")
-            p[self.name("up_proj.bias")] = ParamInfo((self.intermediate_size,), kind="gain", init="normal")
-            p[self.name("down_proj.bias")] = ParamInfo((self.hidden_size,), kind="gain", init="normal")
+            p[n("gate_bias")] = ParamInfo((self.intermediate_size,), kind="gain", init="normal")
+            p[n("up_bias")] = ParamInfo((self.intermediate_size,), kind="gain", init="normal")
+            p[n("down_bias")] = ParamInfo((self.hidden_size,), kind="gain", init="normal")
         return p
 
     def bind(self, tensors):
-        self.w_gate_up = torch.cat([tensors[self.name("gate_proj.weight")],
-                                    tensors[self.name("up_proj.weight")]], dim=0).contiguous()
-        self.w_down = tensors[self.name("down_proj.weight")].contiguous()
+        n = lambda k: tensors[self.name(self.names[k])]
+        self.w_gate_up = torch.cat([n("gate"), n("up")], dim=0).contiguous()
+        self.w_down = n("down").contiguous()
         if self.bias:
-            self.b_gate_up = torch.cat([tensors[self.name("gate_proj.bias")], tensors[self.name("up_proj.bias")]]).contiguous()
-            self.b_down = tensors[self.name("down_proj.bias")].contiguous()
+            self.b_gate_up = torch.cat([n("gate_bias"), n("up_bias")]).contiguous()
+            self.b_down = n("down_bias").contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
         act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
-        if self.bias or not linear_swiglu(x, self.w_gate_up, act, T):
+        # silu: with many rows the product's epilogue makes the activation; relu and few rows: the row kernel
+        if self.bias or self.activation != "silu" or not linear_swiglu(x, self.w_gate_up, act, T):
             gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
                              allow_partial=FUSE_PARTIALS, bias=self.b_gate_up)
-            ops.silu_mul(act, gate_up, T)
+            ops.silu_mul(act, gate_up, T, self.activation)
         return linear(act, self.w_down, ws.get("ffn_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS,
                       bias=self.b_down)
 

@@ -16,17 +16,18 @@ from .base import ParamInfo, Part, ResidualStream, register_part
 class RMSNorm(Part):
     role = "norm"
 
-    def __init__(self, size: int, eps: float, prefix: str, dtype, device):
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", prefix: str = "", dtype=None, device=None):
         super().__init__(prefix, dtype, device)
         self.size = size
         self.eps = float(eps)
+        self.weight_name = weight_name        # "": the gain is the tensor named like the part
         self.gain = None
 
     def parameters(self):
-        return {self.name("weight"): ParamInfo((self.size,), kind="gain", init="ones_normal")}
+        return {self.name(self.weight_name): ParamInfo((self.size,), kind="gain", init="ones_normal")}
 
     def bind(self, tensors):
-        self.gain = tensors[self.name("weight")]
+        self.gain = tensors[self.name(self.weight_name)]
 
     def forward(self, stream: ResidualStream, ctx, tag: str = "normed") -> torch.Tensor:
         out = ctx.workspace.get(tag, stream.rows, self.size, self.dtype)

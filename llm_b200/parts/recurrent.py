@@ -4,8 +4,13 @@
                  token's; o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_{t-1} + k_t v_t^T
   ssd            state-space duality (Mamba-2): a short convolution on x, B, C; S_t = a_t S_{t-1} + dt_t B_t x_t^T,
                  y_t = S_t^T C_t + D x_t with one decay per head and token
-  conv_input     a wrapper: the inner mixer reads h + conv(h), a short causal convolution per channel
-  parallel       a wrapper: two mixers read the same rows; the result is the mean of their RMS-normed outputs
+  hgrn2          a forget gate with a lower bound that also decides what is written: S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,
+                 o_t = S_t^T silu(q_t); no key
+  gated_delta    the gated delta rule: S <- g_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t with unit q, k
+                 behind a short convolution and silu, one decay and one beta per head
+  conv_input     a wrapper: the inner mixer (or feed-forward) reads h + conv(h), a short causal convolution per channel
+  parallel       a wrapper: two mixers read the same rows; the result is the mean of their RMS-normed outputs, or a sum of
+                 the two with fixed scales
 
 None of them keeps keys: a request's past is its state slot (float32, zero at admission), read at the start of
 the step's tokens and written back at their end, so a whole prompt, a portion and a decoded token run the same
@@ -201,6 +206,132 @@ class StateSpaceDuality(Part):
 register_part("mixer", "ssd", StateSpaceDuality)
 
 
+class HGRN2(Part):
+    """Tensors (local names): q, f [H*D, W], f.b and lower [H*D], v [H*V, W], norm [V] (shared by the heads), o [W, H*V].
+    f = lower + (1 - lower) sigmoid(f h + f.b) per head and key channel is the decay, and 1 - f stands where a key would;
+    q passes silu.  Every head's output is RMS-normed over its V values with the plain weight `norm`.  The forget gate's
+    pre-activation is a float32 product; the gate, its complement and the state are float32.  State row: S: H * D * V."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, eps: float, prefix: str = "",
+                 dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if min(hidden_size, num_heads, head_dim, value_dim) <= 0:
+            raise ValueError("hgrn2: sizes must be positive")
+        if head_dim > 256:
+            raise ValueError(f"hgrn2: key size {head_dim} exceeds 256, the most the recurrence kernel takes")
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = int(hidden_size), int(num_heads), int(head_dim), int(value_dim)
+        self.eps = float(eps)
+        self.qk_size, self.v_size = self.num_heads * self.head_dim, self.num_heads * self.value_dim
+        self.w_qv = self.w_f = self.b_f = self.lower = self.gain = self.w_o = None
+
+    def parameters(self):
+        n, W = self.name, self.hidden_size
+        return {n("q"): ParamInfo((self.qk_size, W)), n("f"): ParamInfo((self.qk_size, W)),
+                n("f.b"): ParamInfo((self.qk_size,), kind="gain", init="normal"),
+                n("lower"): ParamInfo((self.qk_size,), kind="gain", init="normal"),
+                n("v"): ParamInfo((self.v_size, W)), n("norm"): ParamInfo((self.value_dim,), kind="gain", init="ones_normal"),
+                n("o"): ParamInfo((W, self.v_size))}
+
+    def bind(self, tensors):
+        t = lambda local: tensors[self.name(local)]
+        self.w_qv = torch.cat([t("q"), t("v")], dim=0).contiguous()
+        self.w_f, self.b_f, self.lower = t("f").contiguous(), t("f.b").contiguous(), t("lower").contiguous()
+        self.gain, self.w_o = t("norm").contiguous(), t("o").contiguous()
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.qk_size * self.value_dim,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        QK, VS = self.qk_size, self.v_size
+        qv = linear(x, self.w_qv, ws.get("hgrn_qv", T, QK + VS, self.dtype), T)
+        z = linear(x, self.w_f, ws.get("hgrn_f", T, QK, torch.float32), T)      # float32: bias, sigmoid and the bound are the kernel's
+        o = ws.get("hgrn_o", T, VS, torch.float32)
+        seg, seg_state, seg_decay = _segments(ctx, "hgrn", QK * self.value_dim, QK)
+        ops.gate_scan(o, qv[:, :QK], qv[:, QK:], z, self.b_f, self.lower, view.state, ctx, self.num_heads, self.head_dim,
+                      self.value_dim, seg_len=seg, seg_state=seg_state, seg_decay=seg_decay)
+        normed = ws.get("attn_out", T, VS, self.dtype)
+        ops.head_rmsnorm_gate(normed, o, self.gain, None, T, self.num_heads, self.eps)
+        return linear(normed, self.w_o, ws.get("mixer_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+
+
+register_part("mixer", "hgrn2", HGRN2)
+
+
+class GatedDeltaRule(Part):
+    """Tensors (local names): q, k [G*D, W], v [H*V, W], each with `<name>.conv` [channels, taps] (a short causal
+    convolution, then silu); b, a [H, W] (beta = sigmoid(b h), decay = exp(-exp(A_log) softplus(a h + dt_bias))); A_log,
+    dt_bias [H]; g [H*V, W] (the output gate, silu); norm [V] (shared by the heads); o [W, H*V].  q and k become unit vectors
+    per head and q is scaled by D^(-1/2).  Head h reads q/k head h // (H / G).  State row: [the convolution's last
+    taps - 1 inputs | S: H * D * V]."""
+
+    role = "mixer"
+
+    def __init__(self, hidden_size: int, num_heads: int, num_qk_heads: int, head_dim: int, value_dim: int, taps: int, eps: float,
+                 unit_eps: float = 1e-6, prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if min(hidden_size, num_heads, num_qk_heads, head_dim, value_dim) <= 0 or not (1 <= taps <= 16):
+            raise ValueError("gated delta rule: sizes must be positive and taps 1 to 16")
+        if num_heads % num_qk_heads:
+            raise ValueError(f"gated delta rule: {num_heads} heads do not divide into {num_qk_heads} key heads")
+        if head_dim > 256:
+            raise ValueError(f"gated delta rule: key size {head_dim} exceeds 256, the most the recurrence kernel takes")
+        self.hidden_size, self.num_heads, self.num_qk_heads = int(hidden_size), int(num_heads), int(num_qk_heads)
+        self.head_dim, self.value_dim, self.taps = int(head_dim), int(value_dim), int(taps)
+        self.eps, self.unit_eps = float(eps), float(unit_eps)
+        self.qk_size, self.v_size = self.num_qk_heads * self.head_dim, self.num_heads * self.value_dim
+        self.conv_channels = 2 * self.qk_size + self.v_size
+        self.conv_cols = _pad4((self.taps - 1) * self.conv_channels)
+        self.w_in = self.w_conv = self.a_log = self.dt_bias = self.gain = self.w_o = None
+
+    def parameters(self):
+        n, W, H = self.name, self.hidden_size, self.num_heads
+        p = {n("q"): ParamInfo((self.qk_size, W)), n("k"): ParamInfo((self.qk_size, W)), n("v"): ParamInfo((self.v_size, W)),
+             n("b"): ParamInfo((H, W)), n("a"): ParamInfo((H, W)), n("g"): ParamInfo((self.v_size, W)),
+             n("A_log"): ParamInfo((H,), kind="gain", init="normal"), n("dt_bias"): ParamInfo((H,), kind="gain", init="normal"),
+             n("norm"): ParamInfo((self.value_dim,), kind="gain", init="ones_normal"), n("o"): ParamInfo((W, self.v_size))}
+        for m, c in (("q", self.qk_size), ("k", self.qk_size), ("v", self.v_size)):
+            p[n(m + ".conv")] = ParamInfo((c, self.taps), kind="gain", init="normal")
+        return p
+
+    def bind(self, tensors):
+        t = lambda local: tensors[self.name(local)]
+        # one product for everything the mixer reads from h: [q | k | v | gate | b | a]
+        self.w_in = torch.cat([t("q"), t("k"), t("v"), t("g"), t("b"), t("a")], dim=0).contiguous()
+        self.w_conv = torch.cat([t("q.conv"), t("k.conv"), t("v.conv")], dim=0).t().contiguous()      # [taps, channels]
+        self.a_log, self.dt_bias = t("A_log").contiguous(), t("dt_bias").contiguous()
+        self.gain, self.w_o = t("norm").contiguous(), t("o").contiguous()
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        return StateNeed((self.conv_cols + self.num_heads * self.head_dim * self.value_dim,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, view) -> torch.Tensor:
+        T, ws = ctx.n_tokens, ctx.workspace
+        QK, VS, C, H = self.qk_size, self.v_size, self.conv_channels, self.num_heads
+        conv_state, S = view.state[:, :self.conv_cols], view.state[:, self.conv_cols:]
+        proj = linear(x, self.w_in, ws.get("delta_in", T, C + VS + 2 * H, self.dtype), T)
+        qkv = ws.get("delta_qkv", T, C, self.dtype)
+        ops.short_conv(qkv, proj[:, :C], self.w_conv, None, conv_state, ctx, silu=True)
+        o = ws.get("delta_o", T, VS, torch.float32)
+        ops.delta_scan(o, qkv[:, :QK], qkv[:, QK:2 * QK], qkv[:, 2 * QK:], proj[:, C + VS:C + VS + H], proj[:, C + VS + H:],
+                       self.a_log, self.dt_bias, S, ctx, H, self.num_qk_heads, self.head_dim, self.value_dim,
+                       self.head_dim ** -0.5, self.unit_eps)
+        normed = ws.get("delta_normed", T, VS, self.dtype)
+        ops.head_rmsnorm_gate(normed, o, self.gain, proj[:, C:C + VS], T, H, self.eps)
+        return linear(normed, self.w_o, ws.get("delta_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)
+
+
+register_part("mixer", "gated_delta", GatedDeltaRule)
+
+
 class ConvInput(Part):
     """The inner mixer reads h + conv(h): conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) per channel, zeros before the
     request's first token, no bias.  Tensor `<prefix>.<weight_name>` [W, taps].  State row: [the last taps - 1
@@ -243,16 +374,59 @@ class ConvInput(Part):
 register_part("mixer", "conv_input", ConvInput)
 
 
+class ConvInputFFN(Part):
+    """The same for a feed-forward: the inner feed-forward reads h + conv(h).  Tensor `<prefix>.<weight_name>` [W, taps].
+    Unlike other feed-forwards this one keeps something per request, the last taps - 1 inputs, and says so with
+    state_need(); the block hands it its columns of the layer's state row."""
+
+    role = "ffn"
+
+    def __init__(self, hidden_size: int, taps: int, inner, weight_name: str = "conv", prefix: str = "", dtype=None, device=None):
+        super().__init__(prefix, dtype, device)
+        if hidden_size <= 0 or not (1 <= taps <= 16):
+            raise ValueError(f"input convolution: width {hidden_size} must be positive and taps {taps} 1 to 16")
+        self.hidden_size, self.taps, self.weight_name = int(hidden_size), int(taps), weight_name
+        self.inner = build_part("ffn", inner, dtype, device)
+        if hasattr(self.inner, "state_need"):
+            raise ValueError("input convolution: the feed-forward inside keeps no state of its own")
+        self.w = None
+
+    def children(self):
+        return [self.inner]
+
+    def parameters(self):
+        return {self.name(self.weight_name): ParamInfo((self.hidden_size, self.taps), kind="gain", init="normal")}
+
+    def bind(self, tensors):
+        self.w = tensors[self.name(self.weight_name)].t().contiguous()            # [taps, width]: a row per tap
+
+    def state_need(self):
+        return StateNeed((max(_pad4((self.taps - 1) * self.hidden_size), 4),), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx, state) -> torch.Tensor:
+        out = ctx.workspace.get("conv_input_ffn", ctx.n_tokens, self.hidden_size, self.dtype)
+        ops.short_conv(out, x, self.w, None, state, ctx, residual=True)
+        return self.inner.forward(out, ctx)
+
+
+register_part("ffn", "conv_input", ConvInputFFN)
+
+
 class ParallelMixers(Part):
     """out = (rms(left(h)) * g_l + rms(right(h)) * g_r) / 2, each RMS norm over the model width with a plain weight
-    (`<prefix>.<left_name>`, `<prefix>.<right_name>`).  At most one side keeps keys (the layer has one cache); the
-    state row is the left side's followed by the right side's."""
+    (`<prefix>.<left_name>`, `<prefix>.<right_name>`); or, with combine="scaled_sum", out = left_scale * left(h) +
+    right_scale * right(h) with two constants and no tensors of its own.  At most one side keeps keys (the layer has one
+    cache); the state row is the left side's followed by the right side's."""
 
     role = "mixer"
 
-    def __init__(self, hidden_size: int, left, right, eps: float, left_name: str = "left.out", right_name: str = "right.out",
-                 prefix: str = "", dtype=None, device=None):
+    def __init__(self, hidden_size: int, left, right, eps: float = 0.0, left_name: str = "left.out", right_name: str = "right.out",
+                 combine: str = "norm_mean", left_scale: float = 1.0, right_scale: float = 1.0, prefix: str = "", dtype=None,
+                 device=None):
         super().__init__(prefix, dtype, device)
+        if combine not in ("norm_mean", "scaled_sum"):
+            raise ValueError(f"parallel mixers: unknown way to combine '{combine}'")
+        self.combine, self.left_scale, self.right_scale = combine, float(left_scale), float(right_scale)
         self.hidden_size, self.eps = int(hidden_size), float(eps)
         self.left_name, self.right_name = left_name, right_name
         self.left, self.right = build_part("mixer", left, dtype, device), build_part("mixer", right, dtype, device)
@@ -267,10 +441,14 @@ class ParallelMixers(Part):
 
     def parameters(self):
         W = self.hidden_size
+        if self.combine == "scaled_sum":
+            return {}
         return {self.name(self.left_name): ParamInfo((W,), kind="gain", init="ones_normal"),
                 self.name(self.right_name): ParamInfo((W,), kind="gain", init="ones_normal")}
 
     def bind(self, tensors):
+        if self.combine == "scaled_sum":
+            return
         self.g_left = tensors[self.name(self.left_name)].contiguous()
         self.g_right = tensors[self.name(self.right_name)].contiguous()
 
@@ -290,7 +468,10 @@ class ParallelMixers(Part):
         a = ops.settle(a, ws.get("parallel_left", T, self.hidden_size, self.dtype), T)
         b = self.right.forward(x, ctx, _sub_view(view, rs))
         out = ws.get("parallel_out", T, self.hidden_size, self.dtype)
-        ops.pair_norm_mean(out, a, b, self.g_left, self.g_right, T, self.eps)
+        if self.combine == "scaled_sum":
+            ops.scaled_sum(out, a, b, self.left_scale, self.right_scale, T)
+        else:
+            ops.pair_norm_mean(out, a, b, self.g_left, self.g_right, T, self.eps)
         return out
 
 
