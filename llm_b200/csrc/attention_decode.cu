@@ -64,7 +64,8 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
                         const T* __restrict__ v_pages, const int* __restrict__ block_table, int table_width,
                         const int* __restrict__ kv_lens, int n_heads, int n_kv, int head_dim_arg, int page_size,
                         int window, float scale, int splits, float softcap, int sink, int keep_first,
-                        const float* __restrict__ sink_values) {
+                        const float* __restrict__ sink_values, const float* __restrict__ dist_r1,
+                        const float* __restrict__ dist_r2, int v_share) {
   constexpr bool STAGE_V = HS > 0;
   constexpr int QW = HS > 0 ? HS : MAX_HS;
   constexpr int V_PITCH = HS + 16 / (int)sizeof(T);                 // elements; rows stay 16-byte aligned
@@ -130,6 +131,12 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
     float acc[GT][2];
 #pragma unroll
     for (int h = 0; h < GT; ++h) acc[h][0] = acc[h][1] = 0.f;
+    float br1[GT], br2[GT];                        // the distance bias of the pass's heads: r1 ln(1 + r2 distance)
+#pragma unroll
+    for (int h = 0; h < GT; ++h) {
+      br1[h] = (dist_r1 && h < nh) ? dist_r1[head0 + h] : 0.f;
+      br2[h] = (dist_r1 && h < nh) ? dist_r2[head0 + h] : 0.f;
+    }
     __syncthreads();
 
     for (int base = k_begin; base < k_end; base += SUB) {
@@ -141,10 +148,15 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
       constexpr int VEC = Row<T>::VEC;
       const int key = tid / KT, part = tid % KT;
       const bool has_key = key < n_sub;
+      int kp = pos;
       if (has_key) {
-        const int u = base + key, kp = u < keep_end ? u : u + skip;
-        const long long row = (((long long)table[kp / page_size] * n_kv + g) * page_size + kp % page_size) * head_dim;
-        if (part == 0) row_s[key] = row;
+        const int u = base + key;
+        kp = u < keep_end ? u : u + skip;
+        const long long page = table[kp / page_size], in_page = kp % page_size;
+        const long long row = ((page * n_kv + g) * page_size + in_page) * head_dim;
+        // v_share neighbouring key heads read one value head (the value pages then hold n_kv / v_share heads)
+        const long long vrow = ((page * (n_kv / v_share) + g / v_share) * page_size + in_page) * head_dim;
+        if (part == 0) row_s[key] = vrow;
         if (STAGE_V) {
           constexpr int PART = (HS > 0 ? HS : KT * VEC) / KT;        // dims of this thread
           constexpr int NV = PART / VEC;
@@ -153,7 +165,7 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
           const T* kr = k_pages + row + part * PART;
 #pragma unroll
           for (int c = 0; c < NV; ++c) {
-            v_raw[c] = *reinterpret_cast<const uint4*>(v_pages + row + part * PART + c * VEC);
+            v_raw[c] = *reinterpret_cast<const uint4*>(v_pages + vrow + part * PART + c * VEC);
             Row<T>::load(kr + c * VEC, kv[c]);
           }
 #pragma unroll
@@ -194,6 +206,7 @@ decode_attention_kernel(T* __restrict__ out, long long out_stride, float* __rest
         s[h] += __shfl_xor_sync(0xffffffffu, s[h], 1);
         s[h] += __shfl_xor_sync(0xffffffffu, s[h], 2);
         if (softcap > 0.f) s[h] = softcap * tanhf(s[h] * inv_cap);
+        if (dist_r1) s[h] -= br1[h] * log1pf(br2[h] * (float)(pos - kp));
         if (!has_key) s[h] = -INFINITY;
       }
       // ---- running maximum per head over the CTA ----
@@ -385,13 +398,18 @@ LLMK_API long long llmk_paged_attention_decode_scratch(int n_entries, int n_head
 // kv_lens[e] = keys of entry e including the new token.  `scratch` holds
 // llmk_paged_attention_decode_scratch(...) floats; its first 4096 words are arrival counters
 // that must be zero when the kernel starts and are zero again when it ends.
-LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const void* q, long long q_stride,
-                                         const void* k_pages, const void* v_pages, const int* block_table,
-                                         int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
-                                         int head_dim, int page_size, int window, float scale, int splits,
-                                         float* scratch, int dtype, cudaStream_t stream, float softcap, int sink,
-                                         int keep_first, const float* sink_values) {
+// dist_r1, dist_r2 (float32 [heads], both or neither): r1[h] ln(1 + r2[h] (query position - key position)) is taken off every
+// capped score.  v_share > 1: v_pages holds n_kv / v_share heads and v_share neighbouring key heads read one of them.
+LLMK_API int llmk_paged_attention_decode_ex(void* out, long long out_stride, const void* q, long long q_stride,
+                                            const void* k_pages, const void* v_pages, const int* block_table,
+                                            int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
+                                            int head_dim, int page_size, int window, float scale, int splits,
+                                            float* scratch, int dtype, cudaStream_t stream, float softcap, int sink,
+                                            int keep_first, const float* sink_values, const float* dist_r1,
+                                            const float* dist_r2, int v_share) {
   if (n_entries == 0) return 0;
+  LLMK_REQUIRE(v_share >= 1 && n_kv % v_share == 0, "attention_decode: %d key heads do not share values in runs of %d", n_kv, v_share);
+  LLMK_REQUIRE((dist_r1 != nullptr) == (dist_r2 != nullptr), "attention_decode: the distance bias takes both of its numbers");
   LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_decode: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
   if (window == 0) keep_first = 0;
   LLMK_REQUIRE(head_dim > 0 && head_dim % 16 == 0 && head_dim <= MAX_HS,
@@ -410,9 +428,20 @@ LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const 
     if (head_dim == 128) kern = decode_attention_kernel<T, 128>;
     launch_kernel(kern, grid, dim3(THREADS), 0, stream, (T*)out, out_stride, scratch, (const T*)q, q_stride,
                   (const T*)k_pages, (const T*)v_pages, block_table, table_width, kv_lens, n_heads, n_kv, head_dim,
-                  page_size, window, scale, splits, softcap, sink, keep_first, sink_values);
+                  page_size, window, scale, splits, softcap, sink, keep_first, sink_values, dist_r1, dist_r2, v_share);
     LLMK_LAUNCH_CHECK("attention_decode");
   });
+}
+
+LLMK_API int llmk_paged_attention_decode(void* out, long long out_stride, const void* q, long long q_stride,
+                                         const void* k_pages, const void* v_pages, const int* block_table,
+                                         int table_width, const int* kv_lens, int n_entries, int n_heads, int n_kv,
+                                         int head_dim, int page_size, int window, float scale, int splits,
+                                         float* scratch, int dtype, cudaStream_t stream, float softcap, int sink,
+                                         int keep_first, const float* sink_values) {
+  return llmk_paged_attention_decode_ex(out, out_stride, q, q_stride, k_pages, v_pages, block_table, table_width, kv_lens,
+                                        n_entries, n_heads, n_kv, head_dim, page_size, window, scale, splits, scratch, dtype,
+                                        stream, softcap, sink, keep_first, sink_values, nullptr, nullptr, 1);
 }
 
 // ---- the variant that allocates nothing (declared in no_alloc.h) ----------------

@@ -79,6 +79,12 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
+__device__ __forceinline__ float fast_lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -123,7 +129,7 @@ struct Smem {
   static constexpr int TOTAL = Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256 /* barriers */;
 };
 
-enum : int { MODE_PLAIN = 0, MODE_EXT = 1, MODE_SIG = 2 };
+enum : int { MODE_PLAIN = 0, MODE_EXT = 1, MODE_SIG = 2, MODE_BIAS = 3 };      // MODE_BIAS: EXT plus the distance bias
 
 template <int HS, int MODE>
 __global__ void __launch_bounds__(THREADS, HS == 64 ? 2 : 1)
@@ -132,8 +138,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int* __restrict__ block_table, int table_width, const int* __restrict__ cu_tokens,
                     const int* __restrict__ kv_lens, int n_entries, int n_heads, int n_kv, int page_size, int n_pages,
                     int window, float scale_log2e, int* __restrict__ err_flag, float cap_c1, float cap_c2, int sink,
-                    int keep_first, const float* __restrict__ head_values, int chunk) {
-  constexpr bool EXT = MODE == MODE_EXT, SIG = MODE == MODE_SIG;
+                    int keep_first, const float* __restrict__ head_values, int chunk, const float* __restrict__ dist_r1,
+                    const float* __restrict__ dist_r2, int v_share) {
+  constexpr bool BIAS = MODE == MODE_BIAS, EXT = MODE == MODE_EXT || BIAS, SIG = MODE == MODE_SIG;
   // cap_c1 = scale / cap and cap_c2 = cap * log2(e) (both 0 without a cap): a score s becomes tanh(s * c1) * c2
   using S = Smem<HS>;
   constexpr int KB = S::KB;
@@ -251,8 +258,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             int page = table[idx];
             page = page < 0 ? 0 : (page >= n_pages ? n_pages - 1 : page);     // pages past the request hold masked keys
             const int off = b * BKV * 128 + pg * page_size * 128;
+            // v_share neighbouring key heads read one value head (the value pages then hold n_kv / v_share heads)
             tma_load_3d((which ? v_s : k_s) + s * S::KV_BYTES + off, which ? &map_v : &map_k, b * 64, 0,
-                        page * n_kv + g, full);
+                        which ? page * (n_kv / v_share) + g / v_share : page * n_kv + g, full);
           }
         }
       }
@@ -324,6 +332,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       float m_ref = (EXT && sink) ? (head_values ? head_values[g * group + head] * 1.4426950408889634f : 0.f) : -INFINITY;
       float l = (EXT && sink) ? 1.f : 0.f;
       const float sig_bias = SIG ? -head_values[g * group + head] * 1.4426950408889634f : 0.f;
+      // the distance bias r1 ln(1 + r2 d) in units of log2: r1 log2(1 + r2 d), taken off the capped score
+      const float br1 = BIAS ? dist_r1[g * group + head] : 0.f, br2 = BIAS ? dist_r2[g * group + head] : 0.f;
       const int keep = EXT ? keep_first : 0;
       const bool capped = EXT && cap_c2 > 0.f;
       bool ok = true;
@@ -410,6 +420,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               xb = fmaf(fast_tanh(__uint_as_float(raw[c][2 * j + 1]) * cap_c1), cap_c2, neg_m);
             } else {
               unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(raw[c][2 * j]), __uint_as_float(raw[c][2 * j + 1])), scale2, neg_m2), xa, xb);
+            }
+            if (BIAS) {
+              // a masked key (behind the row's position) may give the logarithm a negative argument: its weight is set to
+              // zero below whatever it came to
+              const float da = (float)(pos - (key0 + c * 64 + 2 * j));
+              xa = fmaf(-br1, fast_lg2(fmaf(br2, da, 1.f)), xa);
+              xb = fmaf(-br1, fast_lg2(fmaf(br2, da - 1.f, 1.f)), xb);
             }
             float pa = fast_exp2(xa), pb = fast_exp2(xb);
             if (SIG) {
@@ -553,7 +570,8 @@ template <int HS, int MODE>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, long long out_stride,
            const int* block_table, int table_width, const int* cu_tokens, const int* kv_lens, int n_entries,
            int max_tiles, int n_heads, int n_kv, int page_size, int n_pages, int window, float scale_log2e,
-           cudaStream_t stream, float cap_c1, float cap_c2, int sink, int keep_first, const float* head_values, int chunk) {
+           cudaStream_t stream, float cap_c1, float cap_c2, int sink, int keep_first, const float* head_values, int chunk,
+           const float* dist_r1, const float* dist_r2, int v_share) {
   auto kern = attention_tc_kernel<HS, MODE>;
   constexpr int smem = Smem<HS>::TOTAL;
   static bool configured = false;
@@ -565,7 +583,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
   dim3 grid(max_tiles * n_kv);
   launch_kernel(kern, grid, dim3(THREADS), (size_t)smem, stream, mq, mk, mv, (__nv_bfloat16*)out, out_stride, block_table,
                 table_width, cu_tokens, kv_lens, n_entries, n_heads, n_kv, page_size, n_pages, window, scale_log2e, g_attn_err,
-                cap_c1, cap_c2, sink, keep_first, head_values, chunk);
+                cap_c1, cap_c2, sink, keep_first, head_values, chunk, dist_r1, dist_r2, v_share);
   LLMK_LAUNCH_CHECK("attention_tc");
 }
 
@@ -582,12 +600,19 @@ LLMK_API int llmk_attention_tc_supported(int n_heads, int n_kv, int head_dim, in
 // q [n_tokens, q_stride] bf16 with head h at column h*head_dim; out likewise.  cu_tokens
 // [entries + 1] are the entries' row offsets, kv_lens[e] the keys of entry e including its new
 // tokens (which are already in the pages).  k_pages / v_pages [n_pages, n_kv, page_size, head_dim].
-LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
-                               const void* v_pages, int n_pages, const int* block_table, int table_width,
-                               const int* cu_tokens, const int* kv_lens, int n_tokens, int n_entries, int n_heads,
-                               int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream,
-                               float softcap, int sink, int keep_first, const float* head_values, int chunk, int sigmoid) {
+// dist_r1, dist_r2 (float32 [heads], both or neither): r1[h] ln(1 + r2[h] (query position - key position)) is taken off every
+// capped score (softmax weights only).  v_share > 1: v_pages holds n_kv / v_share heads and v_share neighbouring key heads
+// read one of them.
+LLMK_API int llmk_attention_tc_ex(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
+                                  const void* v_pages, int n_pages, const int* block_table, int table_width,
+                                  const int* cu_tokens, const int* kv_lens, int n_tokens, int n_entries, int n_heads,
+                                  int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream,
+                                  float softcap, int sink, int keep_first, const float* head_values, int chunk, int sigmoid,
+                                  const float* dist_r1, const float* dist_r2, int v_share) {
   if (n_tokens == 0 || n_entries == 0) return 0;
+  LLMK_REQUIRE(v_share >= 1 && n_kv % v_share == 0, "attention_tc: %d key heads do not share values in runs of %d", n_kv, v_share);
+  LLMK_REQUIRE((dist_r1 != nullptr) == (dist_r2 != nullptr) && !(dist_r1 && (sigmoid || chunk > 0)),
+               "attention_tc: the distance bias takes both of its numbers and goes with softmax weights and no chunks");
   LLMK_REQUIRE(softcap >= 0.f && keep_first >= 0, "attention_tc: bad soft cap %f or keep_first %d", (double)softcap, keep_first);
   LLMK_REQUIRE(chunk >= 0 && (!sigmoid || (head_values && softcap == 0.f)), "attention_tc: bad chunk %d, or sigmoid weights without their biases or with a soft cap", chunk);
   if (chunk > 0) window = 0;                  // the chunked mask takes the window's place
@@ -606,17 +631,29 @@ LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, l
   int rc;
   if ((rc = get_map3(&mq, q, head_dim, n_heads, n_tokens, head_dim, q_stride, group, tq))) return rc;
   if ((rc = get_map3(&mk, k_pages, head_dim, page_size, (uint64_t)n_pages * n_kv, head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
-  if ((rc = get_map3(&mv, v_pages, head_dim, page_size, (uint64_t)n_pages * n_kv, head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
+  if ((rc = get_map3(&mv, v_pages, head_dim, page_size, (uint64_t)n_pages * (n_kv / v_share), head_dim, (uint64_t)page_size * head_dim, page_size, 1))) return rc;
   const float scale_log2e = scale * 1.4426950408889634f;
   const float c1 = softcap > 0.f ? scale / softcap : 0.f, c2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
 #define LLMK_ATTN_TC(HS, MODE)                                                                                             \
   launch<HS, MODE>(mq, mk, mv, out, out_stride, block_table, table_width, cu_tokens, kv_lens, n_entries, max_tiles, n_heads, \
-                   n_kv, page_size, n_pages, window, scale_log2e, stream, c1, c2, sink, keep_first, head_values, chunk)
+                   n_kv, page_size, n_pages, window, scale_log2e, stream, c1, c2, sink, keep_first, head_values, chunk,       \
+                   dist_r1, dist_r2, v_share)
+  if (dist_r1) return head_dim == 64 ? LLMK_ATTN_TC(64, MODE_BIAS) : LLMK_ATTN_TC(128, MODE_BIAS);
   const bool ext = softcap > 0.f || sink || keep_first > 0 || chunk > 0;
   if (sigmoid) return head_dim == 64 ? LLMK_ATTN_TC(64, MODE_SIG) : LLMK_ATTN_TC(128, MODE_SIG);
   if (head_dim == 64) return ext ? LLMK_ATTN_TC(64, MODE_EXT) : LLMK_ATTN_TC(64, MODE_PLAIN);
   return ext ? LLMK_ATTN_TC(128, MODE_EXT) : LLMK_ATTN_TC(128, MODE_PLAIN);
 #undef LLMK_ATTN_TC
+}
+
+LLMK_API int llmk_attention_tc(void* out, long long out_stride, const void* q, long long q_stride, const void* k_pages,
+                               const void* v_pages, int n_pages, const int* block_table, int table_width,
+                               const int* cu_tokens, const int* kv_lens, int n_tokens, int n_entries, int n_heads,
+                               int n_kv, int head_dim, int page_size, int window, float scale, cudaStream_t stream,
+                               float softcap, int sink, int keep_first, const float* head_values, int chunk, int sigmoid) {
+  return llmk_attention_tc_ex(out, out_stride, q, q_stride, k_pages, v_pages, n_pages, block_table, table_width, cu_tokens,
+                              kv_lens, n_tokens, n_entries, n_heads, n_kv, head_dim, page_size, window, scale, stream, softcap,
+                              sink, keep_first, head_values, chunk, sigmoid, nullptr, nullptr, 1);
 }
 
 // The code the attention kernel left when one of its bounded waits gave up (0 = none).

@@ -968,10 +968,11 @@ def decode_splits(n_entries: int, n_kv: int, max_keys: int, sms: int = 0) -> int
 def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                            block_table: torch.Tensor, kv_lens: torch.Tensor, n_entries: int, n_heads: int,
                            n_kv: int, head_dim: int, window: int, scale: float, splits=None, max_keys: int = 0,
-                           softcap: float = 0.0, sink: bool = False, keep_first: int = 0, sink_values=None) -> None:
+                           softcap: float = 0.0, sink: bool = False, keep_first: int = 0, sink_values=None, dist_bias=None,
+                           v_share: int = 1) -> None:
     """One query token per entry (row e of q), attending to its request's kv_lens[e] keys.
     max_keys: an upper bound of kv_lens, if the host knows one below the table's width.
-    softcap, sink, keep_first: as in paged_attention_generic (the CUDA-core kernel takes them)."""
+    softcap, sink, keep_first, dist_bias, v_share: as in paged_attention_generic (the CUDA-core kernel takes them)."""
     _rows_contig(out, "out"); _rows_contig(q, "q")
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert kv_lens.dtype == torch.int32 and k_pages.is_contiguous() and v_pages.is_contiguous()
@@ -987,13 +988,17 @@ def paged_attention_decode(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Te
     # bfloat16 with a head size of 64 or 128 and pages of a power of two: the query heads of a
     # group as rows of warp-level MMAs (tensor-core library); everything else on the CUDA cores
     assert sink_values is None or (sink_values.dtype == torch.float32 and sink_values.numel() == n_heads)
-    extended = bool(softcap or sink or keep_first)
+    r1, r2 = dist_bias if dist_bias is not None else (None, None)
+    for t in (r1, r2):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
+    assert v_share >= 1 and k_pages.shape[1] == n_kv and v_pages.shape[1] * v_share == n_kv
+    extended = bool(softcap or sink or keep_first or dist_bias is not None or v_share > 1)
     if (not extended and q.dtype == torch.bfloat16 and head_dim in (64, 128) and page & (page - 1) == 0
             and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
         _check_t(load_tensor().llmk_paged_attention_decode_mma(*args, c_int(max_keys), _stream()))
     else:
-        _check(load().llmk_paged_attention_decode(*args, _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
-                                                  c_int(keep_first or 0), _ptr(sink_values)))
+        _check(load().llmk_paged_attention_decode_ex(*args, _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
+                                                     c_int(keep_first or 0), _ptr(sink_values), _ptr(r1), _ptr(r2), c_int(v_share)))
 
 
 def _decode_scratch_floats(n_entries: int, n_heads: int, head_dim: int, splits: int) -> int:
@@ -1052,11 +1057,13 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
                  block_table: torch.Tensor, cu_tokens: torch.Tensor, kv_lens: torch.Tensor, n_tokens: int,
                  n_entries: int, n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
                  softcap: float = 0.0, sink: bool = False, keep_first: int = 0, sink_values=None, chunk: int = 0,
-                 sigmoid_bias=None) -> None:
+                 sigmoid_bias=None, dist_bias=None, v_share: int = 1) -> None:
     """Flash attention on the tensor cores for entries of any length: rows of entry e are
     cu_tokens[e] .. cu_tokens[e+1], its keys (new tokens included) number kv_lens[e].
-    softcap, sink, keep_first, sink_values, chunk, sigmoid_bias: as in paged_attention_generic."""
-    for t in (sink_values, sigmoid_bias):
+    softcap, sink, keep_first, sink_values, chunk, sigmoid_bias, dist_bias, v_share: as in paged_attention_generic."""
+    r1, r2 = dist_bias if dist_bias is not None else (None, None)
+    assert v_share >= 1 and k_pages.shape[1] == n_kv and v_pages.shape[1] * v_share == n_kv
+    for t in (sink_values, sigmoid_bias, r1, r2):
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads)
     assert sink_values is None or sigmoid_bias is None
     _rows_contig(out, "out"); _rows_contig(q, "q")
@@ -1064,18 +1071,21 @@ def attention_tc(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pa
     assert block_table.dim() == 2 and block_table.is_contiguous() and block_table.dtype == torch.int32
     assert cu_tokens.dtype == torch.int32 and kv_lens.dtype == torch.int32
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
-    _check_t(load_tensor().llmk_attention_tc(
+    _check_t(load_tensor().llmk_attention_tc_ex(
         _ptr(out), c_longlong(out.stride(0)), _ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
         c_int(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_tokens), _ptr(kv_lens),
         c_int(n_tokens), c_int(n_entries), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(k_pages.shape[2]),
         c_int(window or 0), c_float(scale), _stream(), c_float(softcap or 0.0), c_int(int(bool(sink))),
         c_int(keep_first or 0), _ptr(sigmoid_bias if sigmoid_bias is not None else sink_values), c_int(chunk or 0),
-        c_int(int(sigmoid_bias is not None))))
+        c_int(int(sigmoid_bias is not None)), _ptr(r1), _ptr(r2), c_int(v_share)))
 
 
 def attention_tc_take_error() -> int:
     """The code the tensor-core attention left when one of its bounded waits gave up (0 = none)."""
     return int(load_tensor().llmk_attention_tc_take_error())
+
+
+ATTENTION_FAST_OPTIONS = True      # False: the distance bias and shared values always run on the general kernel
 
 
 def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: int, head_dim: int,
@@ -1091,8 +1101,26 @@ def paged_attention(out, qkv, k_pages, v_pages, group, ctx, n_heads: int, n_kv: 
     chunked mask, sigmoid weights): the tcgen05 kernel for steps with prompt portions where it takes the sizes; else the
     split-key decode kernel (sink_values) or the general kernel, whose one warp per (token, head) walks at most one chunk.
     dist_bias (a bias that grows with the logarithm of the distance) and v_share (several key heads over one value head):
-    the general kernel."""
+    in bfloat16 with values as wide as keys the split-key decode kernel for single tokens and the tcgen05 kernel for steps
+    with prompt portions, where they take the sizes; the general kernel otherwise."""
     if dist_bias is not None or v_share > 1:
+        same = not value_dim or value_dim == head_dim
+        if ATTENTION_FAST_OPTIONS and same and qkv.dtype == torch.bfloat16 and ctx.decode_only and head_dim % 16 == 0 and head_dim <= 256:
+            max_keys = min(ctx.kv_bucket or 1 << 30, group.block_table.shape[1] * k_pages.shape[2])
+            if window:
+                max_keys = min(max_keys, window + keep_first)
+            splits = max(1, min(16, 2 * decode_splits(ctx.n_entries, n_kv, max_keys), _ceil_div(max_keys, 32)))
+            paged_attention_decode(out, qkv, k_pages, v_pages, group.block_table, ctx.kv_lens, ctx.n_entries, n_heads, n_kv,
+                                   head_dim, window, scale, splits=splits, max_keys=max_keys, softcap=softcap,
+                                   sink=sink or sink_values is not None, keep_first=keep_first, sink_values=sink_values,
+                                   dist_bias=dist_bias, v_share=v_share)
+            return
+        if (ATTENTION_FAST_OPTIONS and same and not ctx.decode_only and qkv.stride(0) % 8 == 0
+                and attention_tc_supported(qkv.dtype, n_heads, n_kv, head_dim, k_pages.shape[2])):
+            attention_tc(out, qkv, k_pages, v_pages, group.block_table, ctx.cu_tokens, ctx.kv_lens, ctx.n_tokens, ctx.n_entries,
+                         n_heads, n_kv, head_dim, window, scale, softcap=softcap, sink=sink or sink_values is not None,
+                         keep_first=keep_first, sink_values=sink_values, dist_bias=dist_bias, v_share=v_share)
+            return
         paged_attention_generic(out, qkv, k_pages, v_pages, group.block_table, ctx.token_entry, ctx.positions,
                                 ctx.n_tokens, n_heads, n_kv, head_dim, window, scale, value_dim=value_dim,
                                 softcap=softcap, sink=sink or sink_values is not None, keep_first=keep_first,

@@ -258,6 +258,57 @@ def test_attention_with_distance_bias_shared_values_and_a_learned_sink(dtype, H,
     assert max_err(out, ref.reshape(T, H * V)) < KTOL[dtype]
 
 
+@pytest.mark.parametrize("H,G,D,share,page,window", [(8, 4, 64, 1, 16, 96), (4, 2, 128, 1, 16, 0), (16, 4, 128, 1, 32, 300), (8, 8, 64, 2, 16, 0),
+                                                     (8, 4, 128, 2, 16, 0), (2, 2, 64, 1, 64, 33)])
+def test_fast_attention_kernels_take_the_distance_bias_and_shared_values(H, G, D, share, page, window):
+    """The tcgen05 kernel on a prompt portion behind cached tokens, and the split-key kernel on single tokens of several
+    requests, against the formula (bfloat16; values as wide as keys)."""
+    from llm_b200.csrc import ops
+    g = torch.Generator().manual_seed(H * 100 + D + share)
+    T, cached, cap, scale = 400, 137, 20.0, 0.2
+    q, k = bf(torch.randn(T, H, D, generator=g)), bf(torch.randn(T, G, D, generator=g))
+    GV = G // share
+    v = bf(torch.randn(T, GV, D, generator=g))
+    r1, r2, sink = torch.rand(H, generator=g) + 0.2, torch.rand(H, generator=g) * 2, torch.randn(H, generator=g)
+    n_pages = -(-T // page)
+    perm = torch.randperm(n_pages + 3, generator=g)[:n_pages]
+    k_pages = torch.zeros(n_pages + 3, G, page, D, dtype=torch.bfloat16)
+    v_pages = torch.zeros(n_pages + 3, GV, page, D, dtype=torch.bfloat16)
+    for t in range(T):
+        k_pages[perm[t // page], :, t % page] = k[t].to(torch.bfloat16)
+        v_pages[perm[t // page], :, t % page] = v[t].to(torch.bfloat16)
+    biased = share == 1
+    dist = (torch.arange(T).unsqueeze(1) - torch.arange(T).unsqueeze(0)).double()
+    seen = (dist >= 0) & ((dist < window) if window else torch.ones_like(dist, dtype=torch.bool))
+    ref = torch.zeros(T, H, D, dtype=torch.float64)
+    for h in range(H):
+        kh = h // (H // G)
+        s = (q[:, h].double() @ k[:, kh].double().T) * scale
+        if biased:
+            s = cap * torch.tanh(s / cap) - r1[h].double() * torch.log1p(r2[h].double() * dist.clamp(min=0))
+        s = s.masked_fill(~seen, float("-inf"))
+        if biased:
+            s = torch.cat([s, sink[h].double().expand(T, 1)], dim=1)
+        ref[:, h] = torch.softmax(s, dim=1)[:, :T] @ v[:, kh // share].double()
+    ref = ref.reshape(T, H * D)
+    opts = dict(softcap=cap, sink=True, sink_values=dev(sink), dist_bias=(dev(r1), dev(r2))) if biased else dict(v_share=share)
+    kd, vd, table = k_pages.cuda(), v_pages.cuda(), i32(perm.tolist()).view(1, -1)
+    # a prompt portion of T - cached tokens behind `cached` tokens that the pages already hold
+    out = torch.zeros(T - cached, H * D, device="cuda", dtype=torch.bfloat16)
+    ops.attention_tc(out, dev(q.reshape(T, H * D)[cached:], "bfloat16"), kd, vd, table, i32([0, T - cached]), i32([T]), T - cached, 1,
+                     H, G, D, window, scale, **opts)
+    assert ops.attention_tc_take_error() == 0
+    assert max_err(out, ref[cached:]) < 1.2e-2          # P is rounded to bfloat16 before the second product
+    # single tokens: four requests over the same pages, at different lengths
+    lens = [T, T - 19, 100, 3]
+    rows = [n - 1 for n in lens]
+    out = torch.zeros(4, H * D, device="cuda", dtype=torch.bfloat16)
+    for splits in (1, 3, 8):
+        ops.paged_attention_decode(out, dev(q.reshape(T, H * D)[rows], "bfloat16"), kd, vd, table.expand(4, -1).contiguous(), i32(lens), 4,
+                                   H, G, D, window, scale, splits=splits, **opts)
+        assert max_err(out, ref[rows]) < KTOL["bfloat16"]
+
+
 # ---- whole models ---------------------------------------------------------------------
 LENGTHS = {"A": [1, 5, 33, 70, 129], "B": [2, 47, 64, 150, 260], "C": [3, 40, 17, 90], "D": [1, 16, 31, 100], "E": [1, 130, 31, 257],
            "F": [2, 33, 140, 95], "G": [1, 2, 60, 75]}
