@@ -453,9 +453,38 @@ NORUSUN_SIZES = {
 }
 
 
+def potipel_config(width, repeats, heads, kv_heads, dim, hgrn_heads, window, delta_heads, delta_kv, ff, experts, top, expert_ff,
+                   vocab=32000):
+    """Layers follow the pattern differential attention, HGRN2, parallel, parallel `repeats` times (a windowed sink attention
+    with a distance bias beside a gated delta rule), dense relu-gated and routed feed-forwards taking turns, three taps of
+    input convolution on every sublayer."""
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "conv": 4,
+                    "mask": {"size": window}},
+           "right": {"heads": delta_heads, "kv_heads": delta_kv, "dim": dim, "vdim": dim, "conv": 4},
+           "left_scale": 0.6, "right_scale": 1.1}
+    kinds = [("attention", {"heads": heads // 2, "kv_heads": max(kv_heads // 2, 1), "dim": dim, "vdim": dim, "scale": dim ** -0.5, "diff": 0.6}),
+             ("hgrn2", {"heads": hgrn_heads, "dim": dim, "vdim": dim}), ("parallel", par), ("parallel", par)]
+    ls = [{"type": t, "mixer": m, "mlp": dense if i % 2 == 0 else moe} for i, (t, m) in enumerate(kinds * repeats)]
+    return {"architecture": "Potipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 16.0},
+            "canon": {"taps": 3}, "layers": ls, "max_position": 4096}
+
+
+# name -> (Potipel config, Fopivik config of the same width, layer runs and heads: the design here that also sets a windowed,
+# capped sink attention beside a gated linear recurrence and routes its feed-forward)
+POTIPEL_SIZES = {
+    "2048": (potipel_config(2048, 2, 16, 4, 128, 16, 1024, 8, 4, 5632, 16, 4, 1408), FOPIVIK_SIZES["2048"][0]),
+    "4096": (potipel_config(4096, 1, 32, 8, 128, 32, 1024, 16, 8, 11008, 32, 4, 2752), FOPIVIK_SIZES["4096"][0]),
+    "1024-head64": (potipel_config(1024, 2, 16, 4, 64, 16, 512, 8, 4, 2816, 8, 2, 1408), FOPIVIK_SIZES["1024-head64"][0]),
+}
+
+
 def design_comparison(args, peaks, design: str = "tevudra") -> int:
-    """Prefill and decode throughput of a design (Tevudra, Fopivik or Norusun) beside Llama at equal layer sizes (random weights,
-    bfloat16), with the device time of every kernel of one prompt step and one decode step.  One JSON line per size."""
+    """Prefill and decode throughput of a design (Tevudra, Fopivik or Norusun) beside Llama at equal layer sizes, or of Potipel
+    beside Fopivik (random weights, bfloat16), with the device time of every kernel of one prompt step and one decode step.
+    One JSON line per size."""
     import collections
 
     import numpy as np
@@ -543,14 +572,15 @@ def design_comparison(args, peaks, design: str = "tevudra") -> int:
         torch.cuda.empty_cache()
         return out
 
-    table = {"fopivik": FOPIVIK_SIZES, "norusun": NORUSUN_SIZES}.get(design, DESIGN_SIZES)
+    table = {"fopivik": FOPIVIK_SIZES, "norusun": NORUSUN_SIZES, "potipel": POTIPEL_SIZES}.get(design, DESIGN_SIZES)
+    beside = "fopivik" if design == "potipel" else "llama"
     sizes = [s for s in table if not args.sizes or s in args.sizes.split(",")]
     for name in sizes:
         tev, lla = table[name]
         sampler = ClockSampler()
         sampler.start()
         res = {"mode": design, "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
-               design: measure(tev), "llama": measure(lla), "peaks": peaks}
+               design: measure(tev), beside: measure(lla), "peaks": peaks}
         res["clocks"] = sampler.stop()
         print(json.dumps(res), flush=True)
     return 0
@@ -568,12 +598,14 @@ def main() -> int:
     ap.add_argument("--no-shapes", action="store_true",
                     help="skip the runs at the Llama-2-7B and Llama-3-8B shapes, the many-request load and the 32-bit check")
     ap.add_argument("--mode", default="all",
-                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra", "fopivik", "norusun"],
+                    choices=["all", "decode", "prefill", "timeline", "timeline_prefill", "decode_attention", "tevudra", "fopivik", "norusun",
+                             "potipel"],
                     help="decode / prefill: only that measurement, for small profiling runs (not the benchmark line); "
                          "timeline: the kernels of one decode layer with their start and end inside the step's CUDA graph; "
                          "decode_attention: the decode attention kernel alone over batches and context lengths "
                          "(--batch with --ctx: that one case); "
-                         "tevudra, fopivik, norusun: that design beside Llama at equal layer sizes, prompt and decode, with every kernel's time")
+                         "tevudra, fopivik, norusun: that design beside Llama at equal layer sizes, prompt and decode, with every kernel's time; "
+                         "potipel: the same beside Fopivik")
     ap.add_argument("--latent", action="store_true", help="decode_attention: the key pages are the value pages too")
     ap.add_argument("--sizes", default="", help="tevudra, fopivik, norusun: which of the sizes to run (comma-separated; default all)")
     ap.add_argument("--ctx", type=int, default=0, help="decode_attention: the context length of the one case to run")
@@ -598,7 +630,7 @@ def main() -> int:
     peaks = load_peaks()
     if args.mode == "decode_attention":
         return decode_attention_sweep(args, peaks, torch, ops)
-    if args.mode in ("tevudra", "fopivik", "norusun"):
+    if args.mode in ("tevudra", "fopivik", "norusun", "potipel"):
         return design_comparison(args, peaks, args.mode)
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     if args.mode != "all":
