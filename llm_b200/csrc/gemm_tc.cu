@@ -806,7 +806,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
               tmem_ld_x32(t_row + (uint32_t)(128 + c), u);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
+              for (int j = 0; j < 32; ++j)       // the gate's activation: silu, or relu where the caller asked for it
+                v[j] = rs.act_plus1 ? fmaxf(__uint_as_float(r[j]), 0.f) * __uint_as_float(u[j])
+                                    : silu_times(__uint_as_float(r[j]), __uint_as_float(u[j]));
             } else {
               tmem_ld_wait();
 #pragma unroll
@@ -1103,6 +1105,10 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
   // product in the epilogue of the pair kernel
   const int act = swiglu >= 2 ? swiglu - 2 : -1;
   if (swiglu >= 2) swiglu = 0;
+  // swiglu == -1: the gated form with relu in silu's place, relu(gate) * up (pair kernel only)
+  const bool relu_gate = swiglu == -1;
+  if (relu_gate) swiglu = 1;
+  LLMK_REQUIRE(!relu_gate || cluster == 3, "gemm_tc: relu(gate) * up in the epilogue needs the pair kernel");
   LLMK_REQUIRE(act < 0 || (cluster == 3 && act <= 3), "gemm_tc: an activation in the epilogue needs the pair kernel (and a kind 0..3)");
   if (swiglu) {
     LLMK_REQUIRE((cluster == 2 || cluster == 3) && !swap && splits == 1 && N % 2 == 0 && (N / 2) % 8 == 0,
@@ -1133,7 +1139,9 @@ LLMK_API int llmk_gemm_tc(const void* A, const void* W, void* C, int M, int N, i
     LLMK_REQUIRE(!swap && splits == 1 && tile % 32 == 0 && tile >= 32 && tile <= 256,
                  "gemm_tc: the pair kernel takes the normal mode, one split and a tile of 32..256 in steps of 32");
     if (swiglu) {
-      if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_SWIGLU>(mp, mq, C, ldc, M, N, K, tile, RopeStore{}, stream);
+      RopeStore gate{};
+      gate.act_plus1 = relu_gate ? 1 : 0;
+      if (out_dtype == LLMK_BF16) return launch_pair<__nv_bfloat16, EPI_SWIGLU>(mp, mq, C, ldc, M, N, K, tile, gate, stream);
       return llmk_fail(-1, "gemm_tc: silu(gate) * up is written as bfloat16 only");
     }
     RopeStore plain{};

@@ -1425,11 +1425,12 @@ def gemm_swiglu_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, r
             and gemm_fast_available(a, w, out, rows))
 
 
-def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> None:
+def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, act: str = "silu") -> None:
     """out[:rows] = silu(a @ gate.T) * (a @ up.T) for w = [gate; up] stacked along its rows
     ([2I, K]), out [rows, I] bfloat16.  One persistent tensor-core kernel: each tile multiplies by
     128 gate rows and their 128 up rows and applies the activation in its epilogue, so the
-    product never reaches memory."""
+    product never reaches memory.  act "relu": relu(gate) * up (the kernel on pairs of CTAs only)."""
+    assert act == "silu" or (act == "relu" and PAIR_GEMM)
     _rows_contig(a, "a"); _rows_contig(w, "w"); _rows_contig(out, "out")
     n, k = w.shape
     assert a.shape[1] == k and out.shape[1] == n // 2 and n % 2 == 0
@@ -1438,7 +1439,7 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) 
     _check_t(load_tensor().llmk_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(rows), c_int(n), c_int(k),
                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
                                c_int(_BF16), c_int(0), c_int(256), c_int(1), c_int(_ceil_div(k, 64)),
-                               c_int(3 if PAIR_GEMM else 2), c_int(1), _stream()))
+                               c_int(3 if PAIR_GEMM else 2), c_int(-1 if act == "relu" else 1), _stream()))
 
 
 def gemm_act_available(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int) -> bool:

@@ -61,8 +61,8 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         T, ws = ctx.n_tokens, ctx.workspace
         act = ws.get("ffn_act", T, self.intermediate_size, self.dtype)
-        # silu: with many rows the product's epilogue makes the activation; relu and few rows: the row kernel
-        if self.bias or self.activation != "silu" or not linear_swiglu(x, self.w_gate_up, act, T):
+        # with many rows the product's epilogue makes the activation; with few rows, or biases, the row kernel
+        if self.bias or not linear_swiglu(x, self.w_gate_up, act, T, self.activation):
             gate_up = linear(x, self.w_gate_up, ws.get("gate_up", T, 2 * self.intermediate_size, self.dtype), T,
                              allow_partial=FUSE_PARTIALS, bias=self.b_gate_up)
             ops.silu_mul(act, gate_up, T, self.activation)

@@ -43,8 +43,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, 
     return res
 
 
-def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> bool:
-    """out[:rows] = silu(x @ gate.T) * (x @ up.T) for weight = [gate; up] stacked along its rows,
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, act: str = "silu") -> bool:
+    """out[:rows] = act(x @ gate.T) * (x @ up.T) for weight = [gate; up] stacked along its rows and act silu or relu,
     with the activation applied in the product's epilogue.  Returns False, having done nothing,
     where that is not possible (float32, shapes the tensor-core kernel refuses, or so few rows
     that the product splits its K dimension): the caller then runs the product and the activation
@@ -53,7 +53,9 @@ def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows
         return True
     if x.dtype != torch.bfloat16 or not ops.gemm_swiglu_available(x, weight, out, rows):
         return False
-    ops.gemm_swiglu(x, weight, out, rows)
+    if act != "silu" and not (act == "relu" and ops.PAIR_GEMM):
+        return False
+    ops.gemm_swiglu(x, weight, out, rows, act)
     return True
 
 

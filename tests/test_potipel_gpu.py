@@ -72,6 +72,18 @@ def test_relu_gated_unit(dtype, ff, rows):
     assert max_err(out, torch.relu(gu[:, :ff]) * gu[:, ff:]) < KTOL[dtype]
 
 
+@pytest.mark.parametrize("rows,ff,width", [(129, 64, 64), (300, 328, 128), (2048, 1024, 512)])
+def test_relu_gate_in_the_products_epilogue(rows, ff, width):
+    """Many rows in bfloat16: relu(gate) * up is made in the epilogue of the gate/up product."""
+    from llm_b200.parts.linear import linear_swiglu
+    g = torch.Generator().manual_seed(rows)
+    x, w = bf(torch.randn(rows, width, generator=g)), bf(torch.randn(2 * ff, width, generator=g) / math.sqrt(width))
+    out = torch.empty(rows, ff, device="cuda", dtype=torch.bfloat16)
+    assert linear_swiglu(dev(x, "bfloat16"), dev(w, "bfloat16"), out, rows, "relu")
+    gu = x.double() @ w.double().T
+    assert max_err(out, torch.relu(gu[:, :ff]) * gu[:, ff:]) < KTOL["bfloat16"]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,R,V", [(4, 1, 8), (6, 3, 14), (2, 2, 96), (8, 4, 64), (3, 3, 130)])
 def test_two_maps_combined_per_head(dtype, H, R, V):
