@@ -456,20 +456,20 @@ NORUSUN_SIZES = {
 def potipel_config(width, repeats, heads, kv_heads, dim, hgrn_heads, window, delta_heads, delta_kv, ff, experts, top, expert_ff,
                    vocab=32000):
     """Layers follow the pattern differential attention, HGRN2, parallel, parallel `repeats` times (a windowed sink attention
-    with a distance bias beside a gated delta rule), dense relu-gated and routed feed-forwards taking turns, three taps of
+    with a distance bias beside a gated delta rule), dense relu-gated and routed feed-forwards taking turns, four taps of
     input convolution on every sublayer."""
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
            "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
-    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0, "conv": 4,
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0, "conv": 4,
                     "mask": {"size": window}},
            "right": {"heads": delta_heads, "kv_heads": delta_kv, "dim": dim, "vdim": dim, "conv": 4},
-           "left_scale": 0.6, "right_scale": 1.1}
-    kinds = [("attention", {"heads": heads // 2, "kv_heads": max(kv_heads // 2, 1), "dim": dim, "vdim": dim, "scale": dim ** -0.5, "diff": 0.6}),
+           "left_scale": 0.8, "right_scale": 0.9}
+    kinds = [("attention", {"heads": heads // 2, "kv_heads": max(kv_heads // 2, 1), "dim": dim, "vdim": dim, "scale": dim ** -0.5, "diff": 0.5}),
              ("hgrn2", {"heads": hgrn_heads, "dim": dim, "vdim": dim}), ("parallel", par), ("parallel", par)]
     ls = [{"type": t, "mixer": m, "mlp": dense if i % 2 == 0 else moe} for i, (t, m) in enumerate(kinds * repeats)]
-    return {"architecture": "Potipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 16.0},
-            "canon": {"taps": 3}, "layers": ls, "max_position": 4096}
+    return {"architecture": "Potipel", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
+            "canon": {"taps": 4}, "layers": ls, "max_position": 4096}
 
 
 # name -> (Potipel config, Fopivik config of the same width, layer runs and heads: the design here that also sets a windowed,

@@ -66,7 +66,7 @@ CONFIG_A = config(64, 200, 3, 4.0, [
 CONFIG_B = config(128, 333, 4, 8.0, [
     layer(parallel(8, 2, 64, 64, size=33, scale=0.125, softcap=30.0, conv=4, r_heads=4, r_kv=1, r_dim=64, r_vdim=32, r_conv=3,
                    left_scale=1.2, right_scale=0.5), dense(64)),
-    layer(attention(4, 1, 64, 64, 0.125, 0.7), moe(64, 1.5, 8, 3, 2, 1)),
+    layer(attention(4, 1, 64, 64, 0.125, 0.7), moe(64, 1.5, 8, 2, 4, 2)),
     layer(hgrn2(4, 32, 64), dense(128)),
     layer(attention(2, 2, 128, 128, 0.09, 0.2), None),
 ], eps=1e-6)
@@ -204,7 +204,7 @@ def random_config(seed: int, large: bool = False) -> dict:
             mixer = hgrn2(rng.randint(1, 6), pick(dims), pick(vdims))
         else:
             kv, r_kv = pick([1, 2, 4]), pick([1, 2, 3])
-            mixer = parallel(kv * rng.randint(1, 3), kv, pick(dims), pick(vdims), size=pick([1, 5, 16, 17, 50, 96, 300]),
+            mixer = parallel(kv * rng.randint(1, 3), kv, pick(dims), pick(vdims), size=pick([1, 5, 16, 17, 50, 80, 300]),
                              scale=rng.uniform(0.05, 0.5), softcap=pick([5.0, 30.0, 50.0]), conv=rng.randint(1, 5),
                              r_heads=r_kv * rng.randint(1, 2), r_kv=r_kv, r_dim=pick(dims), r_vdim=pick(vdims), r_conv=rng.randint(1, 5),
                              left_scale=rng.uniform(0.3, 1.5), right_scale=rng.uniform(0.3, 1.5))
@@ -218,7 +218,7 @@ def random_config(seed: int, large: bool = False) -> dict:
             per = rng.randint(1, 3)
             keep = rng.randint(1, count)
             top = rng.randint(1, keep * per)
-            mlp = moe(pick([64, 96]) if large else pick([8, 12, 20]), pick([0.5, 1.0, 7.0]), count * per, top, count, keep)
+            mlp = moe(pick([64, 80]) if large else pick([8, 12, 20]), pick([0.5, 1.0, 7.0]), count * per, top, count, keep)
         layers.append(layer(mixer, mlp))
     return config(width, pick([61, 128, 200, 333]), rng.randint(1, 6), pick([0.5, 1.0, 4.0, 16.0]), layers, eps=pick([1e-6, 1e-5, 1e-3]))
 

@@ -85,7 +85,7 @@ def test_relu_gate_in_the_products_epilogue(rows, ff, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,R,V", [(4, 1, 8), (6, 3, 14), (2, 2, 96), (8, 4, 64), (3, 3, 130)])
+@pytest.mark.parametrize("H,R,V", [(4, 1, 8), (6, 3, 14), (2, 2, 72), (8, 4, 64), (3, 3, 130)])
 def test_two_maps_combined_per_head(dtype, H, R, V):
     """a1 - lambda a2, the weightless norm, (1 - diff), the sigmoid gate; the maps arrive ordered [group][map][head in group]."""
     from llm_b200.csrc import ops
@@ -107,11 +107,11 @@ def test_scaled_sum_of_two_rows(dtype):
     g = torch.Generator().manual_seed(1)
     a, b = bf(torch.randn(9, 100, generator=g)), bf(torch.randn(9, 100, generator=g))
     out = torch.empty(9, 100, device="cuda", dtype=DT[dtype])
-    ops.scaled_sum(out, dev(a, dtype), dev(b, dtype), 0.6, 1.1, 9)
-    assert max_err(out, 0.6 * a + 1.1 * b) < KTOL[dtype]
+    ops.scaled_sum(out, dev(a, dtype), dev(b, dtype), 0.7, 1.3, 9)
+    assert max_err(out, 0.7 * a + 1.3 * b) < KTOL[dtype]
 
 
-@pytest.mark.parametrize("E,top,count,keep", [(8, 3, 2, 1), (6, 2, 3, 2), (5, 1, 5, 2), (3, 3, 1, 1), (12, 4, 4, 3), (37, 5, 1, 1), (16, 16, 4, 4)])
+@pytest.mark.parametrize("E,top,count,keep", [(8, 2, 2, 1), (6, 2, 3, 2), (5, 1, 5, 2), (3, 3, 1, 1), (12, 4, 4, 3), (37, 5, 1, 1), (16, 16, 4, 4)])
 def test_router_chooses_among_the_best_groups(E, top, count, keep):
     from llm_b200.csrc import ops
     g = torch.Generator().manual_seed(E * 10 + top)
@@ -229,8 +229,8 @@ def test_delta_rule_in_steps_equals_the_plain_loop(dtype, H, G, D, V):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,V,share,page,window", [(4, 4, 16, 8, 2, 16, 0), (8, 4, 48, 96, 2, 16, 0), (6, 2, 10, 14, 1, 8, 19),
-                                                       (8, 4, 64, 64, 1, 16, 96), (2, 2, 24, 16, 1, 32, 50), (12, 6, 64, 64, 2, 16, 0)])
+@pytest.mark.parametrize("H,G,D,V,share,page,window", [(4, 4, 16, 8, 2, 16, 0), (8, 4, 40, 80, 2, 16, 0), (6, 2, 10, 14, 1, 8, 19),
+                                                       (8, 2, 64, 64, 1, 16, 80), (2, 2, 24, 16, 1, 32, 50), (12, 6, 64, 64, 2, 16, 0)])
 def test_attention_with_distance_bias_shared_values_and_a_learned_sink(dtype, H, G, D, V, share, page, window):
     """The general kernel over shuffled pages against the formula: capped scores, r1 ln(1 + r2 distance) taken off, a sink
     with a learned score, a window; with share 2, neighbouring key heads read one value head and there is no bias."""
@@ -270,7 +270,7 @@ def test_attention_with_distance_bias_shared_values_and_a_learned_sink(dtype, H,
     assert max_err(out, ref.reshape(T, H * V)) < KTOL[dtype]
 
 
-@pytest.mark.parametrize("H,G,D,share,page,window", [(8, 4, 64, 1, 16, 96), (4, 2, 128, 1, 16, 0), (16, 4, 128, 1, 32, 300), (8, 8, 64, 2, 16, 0),
+@pytest.mark.parametrize("H,G,D,share,page,window", [(8, 2, 64, 1, 16, 80), (4, 2, 128, 1, 16, 0), (16, 4, 128, 1, 32, 300), (8, 8, 64, 2, 16, 0),
                                                      (8, 4, 128, 2, 16, 0), (2, 2, 64, 1, 64, 33)])
 def test_fast_attention_kernels_take_the_distance_bias_and_shared_values(H, G, D, share, page, window):
     """The tcgen05 kernel on a prompt portion behind cached tokens, and the split-key kernel on single tokens of several
@@ -452,7 +452,7 @@ def _resize(cfg, size):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("size,page", [(16, 16), (17, 16), (15, 16), (33, 8), (96, 16), (50, 32), (2, 16)])
+@pytest.mark.parametrize("size,page", [(16, 16), (17, 16), (15, 16), (33, 8), (80, 16), (50, 32), (2, 16)])
 def test_the_oldest_key_of_the_window_is_seen_and_the_one_before_it_is_not(dtype, size, page):
     cfg, w = _window_model(size)
     T = 260 + 4 * size          # the wider the window, the fewer rows its oldest key wins
