@@ -418,7 +418,7 @@ class PotipelConfig:
     one by one, with a scaled embedding and a short causal convolution added to what every sublayer reads.  Keys:
     `architecture`, `width`, `vocab`, `norm.eps`, `embedding.scale`, `canon.taps`, and per layer `type`, `mixer`, `mlp`
     (`dense` with `ff`; `moe` with `expert.{ff, limit}` and `router.{experts, top, groups.{count, keep}}`; or null) and,
-    optionally, `weights_of`: the index of an earlier layer whose tensors this one uses, with a cache and state of its own.
+    optionally, `weights_of`: the index of another layer whose tensors this one uses, with a cache and state of its own.
     Mixers:
       attention  heads, kv_heads, dim, vdim, scale, diff                      (differential attention, two maps per head)
       hgrn2      heads, dim, vdim
@@ -512,12 +512,23 @@ class PotipelConfig:
                      "mlp": cls._mlp(layer.get("mlp"), where + ".mlp"), "weights_of": None}
             src = layer.get("weights_of")
             if src is not None:
-                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < i) or out[src]["weights_of"] is not None:
-                    raise ConfigError(f"config.json: {where}.weights_of must name an earlier layer that has tensors of its own")
-                if {k: v for k, v in out[src].items() if k != "weights_of"} != {k: v for k, v in entry.items() if k != "weights_of"}:
-                    raise ConfigError(f"config.json: {where} uses the tensors of layer {src} but differs from it")
+                if isinstance(src, bool) or not isinstance(src, int) or not (0 <= src < len(layers)) or src == i:
+                    raise ConfigError(f"config.json: {where}.weights_of must name another layer")
                 entry["weights_of"] = src
             out.append(entry)
+        for i, entry in enumerate(out):          # a layer may name one that names another: the tensors are the last one's
+            src, seen = entry["weights_of"], {i}
+            while src is not None and out[src]["weights_of"] is not None:
+                if src in seen:
+                    raise ConfigError(f"config.json: layers[{i}].weights_of runs in a circle")
+                seen.add(src)
+                src = out[src]["weights_of"]
+            if src is not None and src in seen:
+                raise ConfigError(f"config.json: layers[{i}].weights_of runs in a circle")
+            entry["weights_of"] = src
+            if src is not None and {k: v for k, v in out[src].items() if k != "weights_of"} != \
+                    {k: v for k, v in entry.items() if k != "weights_of"}:
+                raise ConfigError(f"config.json: layers[{i}] uses the tensors of layer {src} but differs from it")
         eos = d.get("eos_token_id")
         cfg = cls(architecture=_take(d, "architecture", str), width=_take(d, "width", int), vocab=_take(d, "vocab", int),
                   norm_eps=_take(norm, "eps", float), embedding_scale=_take(_take(d, "embedding", dict), "scale", float),

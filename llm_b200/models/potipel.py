@@ -57,11 +57,13 @@ def _ffn(cfg: PotipelConfig, ff: dict, prefix: str) -> PartSpec:
 def build_potipel_spec(cfg: PotipelConfig) -> ModelSpec:
     W = cfg.width
     norm = lambda p, q: PartSpec("rmsnorm", {"size": W, "eps": cfg.norm_eps, "weight_name": f"norm{q}"}, p)
-    layers, place, order = [], {}, []
-    for i, layer in enumerate(cfg.layers):
-        if layer["weights_of"] is not None:       # the same parts run again here, with a cache and state of this place
-            order.append(place[layer["weights_of"]])
-            continue
+    own = [i for i, layer in enumerate(cfg.layers) if layer["weights_of"] is None]
+    place = {i: n for n, i in enumerate(own)}       # layer index -> its place among the layers that have tensors
+    # a layer without tensors runs another layer's parts again, with a cache and state of its own place in the order
+    order = [place[i if layer["weights_of"] is None else layer["weights_of"]] for i, layer in enumerate(cfg.layers)]
+    layers = []
+    for i in own:
+        layer = cfg.layers[i]
         p, ff = f"l{i}", layer["mlp"]
         mixer = PartSpec("conv_input", {"hidden_size": W, "taps": cfg.canon_taps, "weight_name": "canon1",
                                         "inner": _mixer(cfg, layer["type"], layer["mixer"], p + ".mix")}, p)
@@ -70,8 +72,6 @@ def build_potipel_spec(cfg: PotipelConfig) -> ModelSpec:
             parts["norm2"] = norm(p, 2)
             parts["ffn"] = PartSpec("conv_input", {"hidden_size": W, "taps": cfg.canon_taps, "weight_name": "canon2",
                                                    "inner": _ffn(cfg, ff, p + ".mlp")}, p)
-        place[i] = len(layers)
-        order.append(place[i])
         layers.append(LayerSpec("prenorm", parts))
     spec = ModelSpec(
         hidden_size=W, vocab_size=cfg.vocab, max_position=cfg.max_position,

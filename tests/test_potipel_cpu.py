@@ -92,6 +92,24 @@ def test_layout_order_caches_and_state_rows():
     assert occ[0].cache_instance != occ[3].cache_instance and occ[2].cache_instance != occ[4].cache_instance
 
 
+def test_a_layer_may_name_one_that_names_another_or_one_that_comes_later():
+    cfg = copy.deepcopy(CONFIGS["A"][0])
+    cfg["layers"].append(dict(cfg["layers"][3], weights_of=3))           # 5 -> 3 -> 0
+    arch, c = parse_config(cfg)
+    assert [l["weights_of"] for l in c.layers] == [None, None, None, 0, 2, 0] and arch.build_spec(c).order == (0, 1, 2, 0, 2, 0)
+    cfg = copy.deepcopy(CONFIGS["A"][0])
+    L = cfg["layers"]
+    L[0], L[3] = L[3], L[0]                                               # the layer with the tensors now comes after its user
+    L[0]["weights_of"] = 3
+    arch, c = parse_config(cfg)
+    spec = arch.build_spec(c)
+    assert spec.order == (2, 0, 1, 2, 1) and sorted(n for n in Model(spec, torch.float32, torch.device("cpu")).parameters() if n.endswith(".norm1")) \
+        == ["l1.norm1", "l2.norm1", "l3.norm1"]
+    cfg["layers"][3]["weights_of"] = 0                                    # a circle
+    with pytest.raises(ConfigError):
+        parse_config(cfg)
+
+
 def test_a_layer_without_feed_forward_keeps_only_its_mixers_state():
     cfg, _ = CONFIGS["D"]
     arch, c = parse_config(cfg)
