@@ -16,6 +16,7 @@
 // Options as in the general kernel: a soft cap on the scaled scores, a sink (one more term of score 0
 // in the denominator, added when the ranges are merged), and, with a window, the request's first
 // keep_first keys, which stay visible: the ranges then run over the kept keys followed by the window's.
+// Also as there: the bias r1 ln(1 + r2 distance) taken off the capped scores, and v_share key heads over one value head.
 #include "common.cuh"
 
 namespace {

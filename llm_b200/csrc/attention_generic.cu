@@ -16,6 +16,9 @@
 // learned number per head (sink_values; it is not scaled); the mask may be by chunks instead of a window (chunk > 0: a
 // query sees the keys at or before it whose position has the same floor(position / chunk)); and the weights may be
 // sigmoid(score + bias[head]) without a softmax (sigmoid_bias given: no maximum, no normalisation, no sink).
+// Two more: a bias that grows with the distance, r1[head] * ln(1 + r2[head] * (position - key position)), taken off the capped
+// score; and key heads that share value heads (v_share neighbouring key heads read one value head: several attention maps,
+// each with keys of its own, over one set of values).
 #include "common.cuh"
 
 namespace {

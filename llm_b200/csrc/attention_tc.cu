@@ -33,6 +33,11 @@
 // (chunk > 0): a row at position p sees the keys floor(p / chunk) * chunk .. p, and the tile walks the blocks from the
 // chunk of its first row on.
 //
+// The BIAS instantiation is EXT with a bias that grows with the distance: r1[head] * log2(1 + r2[head] * (row position - key
+// position)), with lg2.approx.f32, is taken off every capped score in the softmax warps' units of log2 (the block's maximum is
+// still taken over the unbiased scores: it only has to stay within 2^TAU of the row's true maximum or above it).  In every
+// instantiation v_share neighbouring key heads may read one value head: only the producer's value coordinate changes.
+//
 // The SIG instantiation has no softmax: the weight of a visible key is sigmoid(score * scale + head_values[head]), computed
 // in float32 as 1 / (1 + exp2(-x log2 e)) and rounded to bfloat16 for the second product like the softmax's P; there is no
 // maximum, no sum, nothing to rescale and no division at the end.  It takes the chunked mask or the plain causal one.
