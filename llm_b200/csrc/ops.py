@@ -591,6 +591,38 @@ def delta_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
                                   c_float(norm_eps), c_int(_kind(q.dtype)), _stream()))
 
 
+DELTA_CHUNK = 32       # tokens that the chunk-wise delta rule solves together (delta.cu)
+
+
+def delta_chunk_scratch(n_chunks: int, heads: int, dim: int, vdim: int):
+    """Float32 element counts of the chunk-wise delta rule's five scratch buffers for n_chunks chunks."""
+    c = DELTA_CHUNK
+    return [n_chunks * heads * n for n in (dim * 2 * c, c * dim, c * vdim, c * c, 1)]
+
+
+def delta_chunk_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, b: torch.Tensor, a: torch.Tensor,
+                     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, ctx, heads: int, qk_heads: int, dim: int,
+                     vdim: int, q_scale: float, norm_eps: float, scratch) -> None:
+    """delta_scan for a step with prompt portions: the rule chunk by chunk (32 tokens solved together, chunks chained through
+    the state; see delta.cu).  scratch: five flat float32 tensors of at least delta_chunk_scratch(ctx.n_tokens // 32 +
+    ctx.n_entries, ...) elements."""
+    for t in (out, q, k, v, b, a, state):
+        _rows_contig(t, "delta_chunk_scan operand")
+    assert q.stride(0) == k.stride(0) and b.stride(0) == a.stride(0) and q.dtype == k.dtype == v.dtype == b.dtype == a.dtype
+    assert q.shape[1] == k.shape[1] == qk_heads * dim and v.shape[1] == out.shape[1] == heads * vdim
+    assert b.shape[1] == a.shape[1] == heads and out.dtype == state.dtype == torch.float32 and state.shape[1] >= heads * dim * vdim
+    T = ctx.n_tokens
+    for t, numel in zip(scratch, delta_chunk_scratch(T // DELTA_CHUNK + ctx.n_entries, heads, dim, vdim)):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= numel
+    _check(load().llmk_delta_chunk_scan(_ptr(out), c_longlong(out.stride(0)), _ptr(q), _ptr(k), c_longlong(q.stride(0)), _ptr(v),
+                                        c_longlong(v.stride(0)), _ptr(b), _ptr(a), c_longlong(b.stride(0)), _ptr(a_log),
+                                        _ptr(dt_bias), _ptr(state), c_longlong(state.stride(0)), _ptr(ctx.state_slots),
+                                        _ptr(ctx.cu_tokens), c_int(ctx.n_entries), c_int(T), c_int(heads), c_int(qk_heads),
+                                        c_int(dim), c_int(vdim), c_float(q_scale), c_float(norm_eps), *[_ptr(t) for t in scratch],
+                                        c_int(_kind(q.dtype)), _stream()))
+    count_launches(1)
+
+
 def group_rmsnorm_gate(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, rows: int, groups: int,
                        eps: float, gate_first: bool = False) -> None:
     """Per group of channels g: out = rms(x_g) * w_g * silu(gate_g), or with gate_first rms(x_g * silu(gate_g)) * w_g.

@@ -45,6 +45,7 @@ def _state_numel(need) -> int:
 
 
 SEGMENT = 64       # tokens per segment of a prompt step (csrc/scan.cu)
+CHUNKED_DELTA = True      # False: the delta rule walks every step token by token (csrc/delta.cu)
 
 
 def _segments(ctx, tag: str, state_numel: int, decay_numel: int):
@@ -321,9 +322,17 @@ class GatedDeltaRule(Part):
         qkv = ws.get("delta_qkv", T, C, self.dtype)
         ops.short_conv(qkv, proj[:, :C], self.w_conv, None, conv_state, ctx, silu=True)
         o = ws.get("delta_o", T, VS, torch.float32)
-        ops.delta_scan(o, qkv[:, :QK], qkv[:, QK:2 * QK], qkv[:, 2 * QK:], proj[:, C + VS:C + VS + H], proj[:, C + VS + H:],
-                       self.a_log, self.dt_bias, S, ctx, H, self.num_qk_heads, self.head_dim, self.value_dim,
-                       self.head_dim ** -0.5, self.unit_eps)
+        operands = (o, qkv[:, :QK], qkv[:, QK:2 * QK], qkv[:, 2 * QK:], proj[:, C + VS:C + VS + H], proj[:, C + VS + H:],
+                    self.a_log, self.dt_bias, S, ctx, H, self.num_qk_heads, self.head_dim, self.value_dim, self.head_dim ** -0.5,
+                    self.unit_eps)
+        if CHUNKED_DELTA and not ctx.decode_only and T >= 4 * SEGMENT:
+            # a step with prompt portions: chunks of 32 tokens solved together, chained through the state
+            cap = ws.max_rows // ops.DELTA_CHUNK + ctx.cu_tokens.numel()          # chunks of any step: the buffers' sizes
+            scratch = [ws.flat("delta_chunk_" + tag, numel, torch.float32)
+                       for tag, numel in zip(("yq", "k", "w", "b", "g"), ops.delta_chunk_scratch(cap, H, self.head_dim, self.value_dim))]
+            ops.delta_chunk_scan(*operands, scratch)
+        else:
+            ops.delta_scan(*operands)
         normed = ws.get("delta_normed", T, VS, self.dtype)
         ops.head_rmsnorm_gate(normed, o, self.gain, proj[:, C:C + VS], T, H, self.eps)
         return linear(normed, self.w_o, ws.get("delta_out", T, self.hidden_size, self.dtype), T, allow_partial=FUSE_PARTIALS)

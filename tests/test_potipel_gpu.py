@@ -229,6 +229,40 @@ def test_delta_rule_in_steps_equals_the_plain_loop(dtype, H, G, D, V):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,D,V", [(1, 1, 4, 4), (4, 2, 16, 8), (3, 3, 12, 10), (4, 1, 64, 32), (2, 2, 100, 36), (2, 1, 128, 64), (1, 1, 256, 5),
+                                     (6, 2, 8, 130)])
+def test_delta_rule_chunk_by_chunk_equals_the_plain_loop(dtype, H, G, D, V):
+    """A step of three entries (one token, a portion off every chunk border, a long portion) from non-zero states."""
+    from llm_b200.csrc import ops
+    lens, T0 = [1, 77, 300], 40
+    g = torch.Generator().manual_seed(H * 1000 + D + 7)
+    a_log, dt_bias = torch.randn(H, generator=g) * 0.7 - 1.0, torch.randn(H, generator=g) - 1.0
+    state = torch.zeros(4, H * D * V, device="cuda")
+    seqs, refs = [], []
+    for e, n in enumerate(lens):       # every entry: T0 earlier tokens token by token (the state it starts from), then the step
+        T = T0 + n
+        q, k = bf(torch.randn(T, G * D, generator=g)), bf(torch.randn(T, G * D, generator=g))
+        v = bf(torch.randn(T, H * V, generator=g))
+        b, a = bf(torch.randn(T, H, generator=g)), bf(torch.randn(T, H, generator=g))
+        refs.append(_plain_delta(q, k, v, b, a, a_log, dt_bias, H, G, D, V)[T0:])
+        seqs.append((q, k, v, b, a))
+        ctx = step_ctx([T0], [e + 1])
+        ops.delta_scan(torch.empty(T0, H * V, device="cuda"), dev(q[:T0], dtype), dev(k[:T0], dtype), dev(v[:T0], dtype), dev(b[:T0], dtype),
+                       dev(a[:T0], dtype), dev(a_log), dev(dt_bias), state, ctx, H, G, D, V, D ** -0.5)
+    cat = lambda i: dev(torch.cat([sq[i][T0:] for sq in seqs]), dtype)
+    T = sum(lens)
+    ctx = step_ctx(lens, [1, 2, 3])
+    out = torch.empty(T, H * V, device="cuda")
+    scratch = [torch.full((numel,), float("nan"), device="cuda") for numel in ops.delta_chunk_scratch(T // 32 + len(lens), H, D, V)]
+    walked = state.clone()
+    ops.delta_chunk_scan(out, cat(0), cat(1), cat(2), cat(3), cat(4), dev(a_log), dev(dt_bias), state, ctx, H, G, D, V, D ** -0.5, 1e-6, scratch)
+    assert max_err(out, torch.cat(refs)) < 3e-5
+    out2 = torch.empty(T, H * V, device="cuda")
+    ops.delta_scan(out2, cat(0), cat(1), cat(2), cat(3), cat(4), dev(a_log), dev(dt_bias), walked, ctx, H, G, D, V, D ** -0.5)
+    assert max_err(state, walked) < 3e-5 and float(state[0].abs().max()) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,V,share,page,window", [(4, 4, 16, 8, 2, 16, 0), (8, 4, 40, 80, 2, 16, 0), (6, 2, 10, 14, 1, 8, 19),
                                                        (8, 2, 64, 64, 1, 16, 80), (2, 2, 24, 16, 1, 32, 50), (12, 6, 64, 64, 2, 16, 0)])
 def test_attention_with_distance_bias_shared_values_and_a_learned_sink(dtype, H, G, D, V, share, page, window):
